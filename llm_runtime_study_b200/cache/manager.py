@@ -40,6 +40,12 @@ class StateArray:
     layer: int
     requirement: FixedState
 
+    @property
+    def key(self):
+        """Where the manager keeps the array: the layer, or (layer, name) for a state with a name of its own."""
+
+        return self.layer if self.requirement.name == "state" else (self.layer, self.requirement.name)
+
 
 @dataclass(frozen=True)
 class CacheLayout:
@@ -55,13 +61,21 @@ class CacheLayout:
 
         by_need: dict[PagedTensors, list[int]] = {}
         states = []
-        for layer, need in enumerate(requirements):
-            if isinstance(need, PagedTensors):
-                by_need.setdefault(need, []).append(layer)
-            elif isinstance(need, FixedState):
-                states.append(StateArray(layer, need))
-            elif need is not None:
-                raise KVCacheError(f"layer {layer} asks for an unknown kind of cache: {need!r}")
+        for layer, needs in enumerate(requirements):
+            # a mixer may ask for several things at once: pages and arrays of fixed size, or several arrays
+            needs = needs if isinstance(needs, (tuple, list)) else (needs,)
+            if sum(isinstance(need, PagedTensors) for need in needs) > 1:
+                raise KVCacheError(f"layer {layer} asks for pages twice: a layer belongs to one group of pages")
+            names = [need.name for need in needs if isinstance(need, FixedState)]
+            if len(names) != len(set(names)):
+                raise KVCacheError(f"layer {layer} asks for two arrays of fixed size under one name: {names}")
+            for need in needs:
+                if isinstance(need, PagedTensors):
+                    by_need.setdefault(need, []).append(layer)
+                elif isinstance(need, FixedState):
+                    states.append(StateArray(layer, need))
+                elif need is not None:
+                    raise KVCacheError(f"layer {layer} asks for an unknown kind of cache: {need!r}")
         groups = tuple(PageGroup(need, tuple(layers)) for need, layers in by_need.items())
         return cls(groups, tuple(states))
 
@@ -73,7 +87,11 @@ class LayerCache:
     group: int | None = None            # page group index
     tensors: dict = field(default_factory=dict)   # name -> this layer's pages of that tensor, [pages, ...]
     page_size: int = 0
-    state: torch.Tensor | None = None   # [slots, *shape] for fixed-size state
+    states: dict = field(default_factory=dict)    # name -> [slots, *shape] for fixed-size state
+
+    @property
+    def state(self) -> torch.Tensor | None:     # the array a mixer with a single ``FixedState`` asked for
+        return self.states.get("state", next(iter(self.states.values()), None))
 
     @property
     def keys(self) -> torch.Tensor | None:      # [pages, kv_heads, page_size, head_dim]
@@ -207,10 +225,13 @@ class CacheManager:
         # Fixed-size state: one row per request slot and one more that belongs to nobody, for the rows that
         # pad a batch up to the size of its captured graph (what a mixer writes there is never read).
         self.padding_slot = max_requests
-        self.state_arrays: dict[int, torch.Tensor] = {
-            s.layer: torch.zeros((max_requests + 1, *s.requirement.shape), dtype=s.requirement.dtype, device=self.device)
+        self.state_arrays: dict = {
+            s.key: torch.zeros((max_requests + 1, *s.requirement.shape), dtype=s.requirement.dtype, device=self.device)
             for s in layout.states
         }
+        self._layer_states: dict[int, dict[str, torch.Tensor]] = {}
+        for s in layout.states:
+            self._layer_states.setdefault(s.layer, {})[s.requirement.name] = self.state_arrays[s.key]
         self.slots = SlotTable(max_requests, self.device)
         self._layer_group = {layer: (g, i) for g, group in enumerate(layout.groups) for i, layer in enumerate(group.layers)}
         self._free_slots = list(range(max_requests - 1, -1, -1))
@@ -232,13 +253,13 @@ class CacheManager:
     def layer_cache(self, layer: int) -> LayerCache:
         """The cache view of a layer that owns one."""
 
+        states = dict(self._layer_states.get(layer, {}))
         if layer in self._layer_group:
             g, i = self._layer_group[layer]
             pool = self.groups[g]
-            return LayerCache(group=g, tensors={name: t[i] for name, t in pool.tensors.items()}, page_size=pool.page_size)
-        if layer in self.state_arrays:
-            return LayerCache(state=self.state_arrays[layer])
-        return LayerCache()
+            return LayerCache(group=g, tensors={name: t[i] for name, t in pool.tensors.items()}, page_size=pool.page_size,
+                              states=states)
+        return LayerCache(states=states)
 
     @property
     def num_bytes(self) -> int:

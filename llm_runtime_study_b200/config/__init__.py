@@ -1,5 +1,6 @@
 from .fields import read_config_dict, required, optional
 from .qwen3 import Qwen3Config
+from .sorulix import SorulixConfig
 from .registry import (
     Architecture,
     architecture_for,
@@ -11,6 +12,7 @@ from .registry import (
 __all__ = [
     "Architecture",
     "Qwen3Config",
+    "SorulixConfig",
     "architecture_for",
     "load_config",
     "optional",

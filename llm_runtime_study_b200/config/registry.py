@@ -26,12 +26,16 @@ class Architecture:
     descriptions, the order in which they run, and the embedding/head/norm
     descriptions) from which the generic model is built; it names part kinds
     only, never sizes of its own.
+    ``describe_for_checkpoint(config, shapes)`` (optional) does the same for an
+    architecture some of whose sizes are given by the stored tensors' shapes
+    (``shapes``: name -> shape) rather than by ``config.json``.
     """
 
     name: str
     model_type: str
     config_from_dict: Callable[[Mapping[str, Any]], Any]
     describe: Callable[[Any], Any]
+    describe_for_checkpoint: Callable[[Any, Mapping[str, tuple]], Any] | None = None
 
 
 _BY_NAME: dict[str, Architecture] = {}
@@ -51,7 +55,7 @@ def registered_architectures() -> tuple[str, ...]:
 
 def architecture_for(raw: Mapping[str, Any]) -> Architecture:
     """Pick the entry by ``model_type`` (as the reference does), else by
-    ``architectures[0]``."""
+    ``architectures[0]``, else by ``architecture`` (a single name)."""
 
     model_type = raw.get("model_type")
     if isinstance(model_type, str) and model_type in _BY_MODEL_TYPE:
@@ -59,6 +63,11 @@ def architecture_for(raw: Mapping[str, Any]) -> Architecture:
     names = raw.get("architectures")
     if isinstance(names, list) and names and isinstance(names[0], str) and names[0] in _BY_NAME:
         return _BY_NAME[names[0]]
+    name = raw.get("architecture")
+    if isinstance(name, str) and name in _BY_NAME:
+        return _BY_NAME[name]
+    if isinstance(name, str) and "model_type" not in raw:
+        raise ConfigError(f"unsupported architecture {name!r}; expected one of: {', '.join(sorted(_BY_NAME))}")
     if "model_type" not in raw:
         raise ConfigError("missing required configuration field: model_type")
     supported = ", ".join(sorted(_BY_MODEL_TYPE))

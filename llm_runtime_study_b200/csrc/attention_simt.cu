@@ -8,6 +8,11 @@
 // Formula (mini_llm/nn/attention.py:95-99, 231-248): S = q.k^T * scale, key t visible
 // iff t <= p (and t > p - window when a window is set), P = softmax(S), o = P.v;
 // query head j reads KV head j / (nq / nkv)  (mini_llm/nn/attention.py:18-33).
+//
+// Optional rules on the scores, each a parameter: a soft cap (S <- cap * tanh(S / cap)), a
+// bias by distance (S <- S - slope_j * (p - t) with one slope per query head), and a sink
+// (a virtual key of score 0 that carries no value: the weights become exp(S) / (1 + sum exp(S))).
+// Values may have a head size `dv` of their own.
 #include "common.cuh"
 
 namespace b200 {
@@ -20,7 +25,8 @@ paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_poo
                             const T* __restrict__ v_pool, T* __restrict__ out,
                             const int* __restrict__ positions, const int* __restrict__ token_entry,
                             const int* __restrict__ block_table, int table_stride, int page_size,
-                            int nq, int nkv, int d, float scale, int window) {
+                            int nq, int nkv, int d, float scale, int window, int dv, float softcap,
+                            const float* __restrict__ slopes, int sink) {
   extern __shared__ float smem[];
   pdl_trigger();
   pdl_wait();
@@ -37,7 +43,10 @@ paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_poo
   __syncwarp();
 
   const int w0 = window > 0 ? max(0, p - window + 1) : 0;
-  float m = -INFINITY, l = 0.f;
+  // the sink is a key of score 0 and value 0 that every row sees: it starts the running maximum and sum
+  float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;
+  const float slope = slopes ? slopes[head] : 0.f;
+  const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
   float acc[kMaxChunks];
 #pragma unroll
   for (int c = 0; c < kMaxChunks; ++c) acc[c] = 0.f;
@@ -59,6 +68,8 @@ paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_poo
         for (int e = 0; e < VN; ++e) dot = fmaf(qs[i + e], f[e], dot);
       }
       s = dot * scale;
+      if (softcap > 0.f) s = softcap * tanhf(s * inv_cap);
+      s -= slope * static_cast<float>(p - t);
     }
     const float m_tile = warp_max(s);
     if (m_tile == -INFINITY) continue;
@@ -74,35 +85,38 @@ paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_poo
       if (pj == 0.f) continue;
       const int tj = t0 + j;
       const int page = table[tj / page_size];
-      const T* vrow = v_pool + ((static_cast<size_t>(page) * nkv + kvh) * page_size + tj % page_size) * d;
+      const T* vrow = v_pool + ((static_cast<size_t>(page) * nkv + kvh) * page_size + tj % page_size) * dv;
 #pragma unroll
       for (int c = 0; c < kMaxChunks; ++c) {
         const int i = lane + 32 * c;
-        if (i < d) acc[c] = fmaf(pj, to_float(vrow[i]), acc[c]);
+        if (i < dv) acc[c] = fmaf(pj, to_float(vrow[i]), acc[c]);
       }
     }
     m = m_new;
   }
-  T* orow = out + (static_cast<size_t>(token) * nq + head) * d;
+  T* orow = out + (static_cast<size_t>(token) * nq + head) * dv;
   const float inv = l > 0.f ? 1.f / l : 0.f;   // a row without any visible key (padding) gives zeros
 #pragma unroll
   for (int c = 0; c < kMaxChunks; ++c) {
     const int i = lane + 32 * c;
-    if (i < d) orow[i] = from_float<T>(acc[c] * inv);
+    if (i < dv) orow[i] = from_float<T>(acc[c] * inv);
   }
 }
 
 }  // namespace b200
 
-extern "C" int b200_paged_attention_simt(
+// q [n, nq, d], keys [pages, nkv, page_size, d], values [pages, nkv, page_size, dv], out [n, nq, dv].
+// softcap <= 0: no cap; slopes (nq floats) may be null; sink 0 or 1.
+extern "C" int b200_paged_attention_simt_rules(
     const void* q, const void* k_pool, const void* v_pool, void* out, const int* positions,
     const int* token_entry, const int* block_table, int table_stride, int page_size, int n,
-    int nq, int nkv, int d, float scale, int window, int dtype, cudaStream_t stream) {
+    int nq, int nkv, int d, int dv, float scale, int window, float softcap, const float* slopes, int sink,
+    int dtype, cudaStream_t stream) {
   using namespace b200;
   if (n <= 0) return 0;
-  if (d <= 0 || d % 8 != 0 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0)
+  if (d <= 0 || d % 8 != 0 || dv <= 0 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0)
     return B200_ERR_BAD_SIZE;
-  if (d > 32 * kMaxChunks) return B200_ERR_TOO_LARGE;
+  if (d > 32 * kMaxChunks || dv > 32 * kMaxChunks) return B200_ERR_TOO_LARGE;
   dim3 grid(n, (nq + 3) / 4);
   if (grid.y > 65535) return B200_ERR_TOO_LARGE;
   const size_t smem = static_cast<size_t>(4) * d * sizeof(float);
@@ -110,6 +124,14 @@ extern "C" int b200_paged_attention_simt(
       launch(paged_attention_simt_kernel<T>, dim3(grid), dim3(128), smem, stream, 
           static_cast<const T*>(q), static_cast<const T*>(k_pool), static_cast<const T*>(v_pool),
           static_cast<T*>(out), positions, token_entry, block_table, table_stride, page_size, nq,
-          nkv, d, scale, window));
+          nkv, d, scale, window, dv, softcap, slopes, sink));
   return launch_status();
+}
+
+extern "C" int b200_paged_attention_simt(
+    const void* q, const void* k_pool, const void* v_pool, void* out, const int* positions,
+    const int* token_entry, const int* block_table, int table_stride, int page_size, int n,
+    int nq, int nkv, int d, float scale, int window, int dtype, cudaStream_t stream) {
+  return b200_paged_attention_simt_rules(q, k_pool, v_pool, out, positions, token_entry, block_table, table_stride,
+                                         page_size, n, nq, nkv, d, d, scale, window, 0.f, nullptr, 0, dtype, stream);
 }

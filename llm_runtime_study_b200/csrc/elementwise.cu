@@ -711,3 +711,138 @@ extern "C" int b200_qk_norm_rope_write(
           static_cast<T*>(k_pool), static_cast<T*>(v_pool), nq, nkv, d, qkv_stride));
   return launch_status();
 }
+
+// ------------------------------------------------------------------------------------------
+// Kernels for layers that normalise q and k over the whole projection, gate a feed-forward
+// with limits, average several normalised branches, or add rows into the residual stream.
+namespace b200 {
+
+// One CTA per token.  Row layout [q: nq*d | k: nkv*d | v: nkv*dv].  q and k are each normalised
+// over their whole width (all heads at once): x * rsqrt(mean(x^2) + eps) * w, q then scaled by the
+// position's temperature 1 + coef * ln(floor((p + 1) / every) + 1) (every = 0: none); q goes to
+// q_out [n, nq*d], k and v into the pages at the token's position.  A null weight leaves that part
+// as it is.
+template <typename T>
+__global__ void qk_rownorm_write_kernel(const T* __restrict__ qkv, int ld, T* __restrict__ q_out,
+                                        const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+                                        float temp_coef, int temp_every, const int* __restrict__ positions,
+                                        const int* __restrict__ token_entry, const int* __restrict__ block_table,
+                                        int table_stride, int page_size, T* __restrict__ k_pool, T* __restrict__ v_pool,
+                                        int nq, int nkv, int d, int dv) {
+  __shared__ float scratch[32];
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int qw = nq * d, kw = nkv * d, vw = nkv * dv;
+  const T* row = qkv + static_cast<size_t>(t) * ld;
+  const int p = positions[t];
+  float ssq = 0.f, ssk = 0.f;
+  for (int i = threadIdx.x; i < qw; i += blockDim.x) { const float x = to_float(row[i]); ssq = fmaf(x, x, ssq); }
+  for (int i = threadIdx.x; i < kw; i += blockDim.x) { const float x = to_float(row[qw + i]); ssk = fmaf(x, x, ssk); }
+  const float fq = q_w ? rsqrtf(block_sum(ssq, scratch) / static_cast<float>(qw) + eps) : 1.f;
+  const float fk = k_w ? rsqrtf(block_sum(ssk, scratch) / static_cast<float>(kw) + eps) : 1.f;
+  const float temp = temp_every > 0 ? 1.f + temp_coef * logf(static_cast<float>((p + 1) / temp_every) + 1.f) : 1.f;
+  for (int i = threadIdx.x; i < qw; i += blockDim.x)
+    q_out[static_cast<size_t>(t) * qw + i] = from_float<T>(to_float(row[i]) * fq * (q_w ? q_w[i] : 1.f) * temp);
+  const int page = block_table[static_cast<size_t>(token_entry[t]) * table_stride + p / page_size];
+  if (page < 0) return;           // a padding row has no pages
+  const size_t at = static_cast<size_t>(page) * nkv * page_size + p % page_size;
+  for (int i = threadIdx.x; i < kw; i += blockDim.x) {
+    const int g = i / d, c = i % d;
+    k_pool[(at + static_cast<size_t>(g) * page_size) * d + c] = from_float<T>(to_float(row[qw + i]) * fk * (k_w ? k_w[i] : 1.f));
+  }
+  for (int i = threadIdx.x; i < vw; i += blockDim.x) {
+    const int g = i / dv, c = i % dv;
+    v_pool[(at + static_cast<size_t>(g) * page_size) * dv + c] = row[qw + kw + i];
+  }
+}
+
+// rows [gate | up], each `inter` wide: g = min(gate, limit), u = clamp(up, -limit, limit),
+// out = g * sigmoid(alpha * g) * (u + 1)
+template <typename T>
+__global__ void glu_limit_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, float limit, float alpha) {
+  pdl_trigger();
+  pdl_wait();
+  const T* row = gate_up + static_cast<size_t>(blockIdx.x) * 2 * inter;
+  for (int i = threadIdx.x; i < inter; i += blockDim.x) {
+    const float g = fminf(to_float(row[i]), limit);
+    const float u = fminf(fmaxf(to_float(row[inter + i]), -limit), limit);
+    out[static_cast<size_t>(blockIdx.x) * inter + i] = from_float<T>(g / (1.f + expf(-alpha * g)) * (u + 1.f));
+  }
+}
+
+// out[t] (+)= factor * x[t] * rsqrt(mean(x[t]^2) + eps) * w
+__global__ void rmsnorm_accumulate_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ out,
+                                          int hidden, float eps, float factor, int accumulate) {
+  __shared__ float scratch[32];
+  pdl_trigger();
+  pdl_wait();
+  const float* row = x + static_cast<size_t>(blockIdx.x) * hidden;
+  float* dst = out + static_cast<size_t>(blockIdx.x) * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) ss = fmaf(row[i], row[i], ss);
+  const float f = rsqrtf(block_sum(ss, scratch) / static_cast<float>(hidden) + eps) * factor;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float y = row[i] * f * w[i];
+    dst[i] = accumulate ? dst[i] + y : y;
+  }
+}
+
+// resid[t] += a[t] + b[t] + vec, each optional
+__global__ void add_rows_kernel(float* __restrict__ resid, const float* __restrict__ a, const float* __restrict__ b,
+                                const float* __restrict__ vec, int hidden) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t base = static_cast<size_t>(blockIdx.x) * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float x = resid[base + i];
+    if (a) x += a[base + i];
+    if (b) x += b[base + i];
+    if (vec) x += vec[i];
+    resid[base + i] = x;
+  }
+}
+
+}  // namespace b200
+
+extern "C" int b200_qk_rownorm_write(const void* qkv, int ld, void* q_out, const float* q_w, const float* k_w, float eps,
+                                     float temp_coef, int temp_every, const int* positions, const int* token_entry,
+                                     const int* block_table, int table_stride, int page_size, void* k_pool, void* v_pool,
+                                     int n, int nq, int nkv, int d, int dv, int dtype, cudaStream_t stream) {
+  using namespace b200;
+  if (n <= 0) return 0;
+  if (nq <= 0 || nkv <= 0 || d <= 0 || dv <= 0 || page_size <= 0 || ld < nq * d + nkv * (d + dv)) return B200_ERR_BAD_SIZE;
+  B200_DISPATCH_DTYPE(dtype, T, launch(qk_rownorm_write_kernel<T>, dim3(n), dim3(256), 0, stream, static_cast<const T*>(qkv), ld,
+                                       static_cast<T*>(q_out), q_w, k_w, eps, temp_coef, temp_every, positions, token_entry,
+                                       block_table, table_stride, page_size, static_cast<T*>(k_pool), static_cast<T*>(v_pool),
+                                       nq, nkv, d, dv));
+  return launch_status();
+}
+
+extern "C" int b200_glu_limit(const void* gate_up, void* out, int n, int inter, float limit, float alpha, int dtype,
+                              cudaStream_t stream) {
+  using namespace b200;
+  if (n <= 0) return 0;
+  if (inter <= 0) return B200_ERR_BAD_SIZE;
+  B200_DISPATCH_DTYPE(dtype, T, launch(glu_limit_kernel<T>, dim3(n), dim3(256), 0, stream, static_cast<const T*>(gate_up),
+                                       static_cast<T*>(out), inter, limit, alpha));
+  return launch_status();
+}
+
+extern "C" int b200_rmsnorm_accumulate(const float* x, const float* w, float* out, int n, int hidden, float eps, float factor,
+                                       int accumulate, cudaStream_t stream) {
+  using namespace b200;
+  if (n <= 0) return 0;
+  if (hidden <= 0) return B200_ERR_BAD_SIZE;
+  launch(rmsnorm_accumulate_kernel, dim3(n), dim3(256), 0, stream, x, w, out, hidden, eps, factor, accumulate);
+  return launch_status();
+}
+
+extern "C" int b200_add_rows(float* resid, const float* a, const float* b, const float* vec, int n, int hidden,
+                             cudaStream_t stream) {
+  using namespace b200;
+  if (n <= 0) return 0;
+  if (hidden <= 0) return B200_ERR_BAD_SIZE;
+  launch(add_rows_kernel, dim3(n), dim3(256), 0, stream, resid, a, b, vec, hidden);
+  return launch_status();
+}

@@ -1,0 +1,353 @@
+// Mixers that carry a state of fixed size per request instead of a growing cache:
+//
+//   linear scan     S_t = D_t S_(t-1) + k_t u_t^T,  o_t = S_t^T q_t        per head, S is [d, dv]
+//                   D_t = one decay per head (a constant), or a diagonal of per-row factors g_t (gated)
+//                   u_t = v_t (plain), or beta_t (v_t - (D_t S_(t-1))^T k_t) (delta rule)
+//   short convolution over time per channel, with the last taps-1 inputs kept per request
+//   per-group RMS norm of the read-out times a sigmoid gate
+//
+// The state, the decays, the gates of the recurrence and the unit norms are float32 whatever the
+// storage type of the projections.  Tokens of one request are processed in order, one after the
+// other, from the state the request's slot holds, so a token's result does not depend on how the
+// sequence was cut into steps or on what else is in the batch.
+#include "common.cuh"
+
+namespace b200 {
+
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
+__device__ __forceinline__ float silu_f(float x) { return x * sigmoid_f(x); }
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+// ---------------------------------------------------------------------------- linear scan
+struct ScanParams {
+  const void* q; const void* k; const void* v;   // rows of the storage type; heads side by side
+  int ldq, ldk, ldv;                              // row strides in elements
+  const float* gate; int ldg;                     // [n, H * d] per-row factors (gated) or null
+  const float* decay;                             // [H] constant factors (not gated)
+  const float* beta; int ldb;                     // [n, H] (delta rule) or null
+  float* state;                                   // [slots, H, d, dv]
+  float* out; int ldo;                            // [n, H * dv]
+  const int* q_start; const int* slots;           // per entry: first token, request slot
+  int H, Hqk, d, dv, act, rl;                     // act 1: silu on q, k, v as they are read; rl: lanes that share a column
+};
+
+constexpr int kScanThreads = 128;
+constexpr int kScanChunk = 8;     // tokens staged in shared memory at a time
+
+// One CTA owns some columns of one head's state for one request.  A column is independent of the
+// others: S[:, c] <- D S[:, c] + k u_c.  Its d rows are spread over `rl` lanes of one warp (row i
+// belongs to lane i % rl), DPT rows per lane in registers; the two dot products over rows are
+// finished by shuffles.
+template <typename T, int DPT, bool DELTA, bool GATED>
+__global__ void __launch_bounds__(kScanThreads) linear_scan_kernel(const ScanParams p) {
+  extern __shared__ float smem[];
+  pdl_trigger();
+  pdl_wait();
+  const int rl = p.rl, cols_per_warp = 32 / rl, cols = (kScanThreads / 32) * cols_per_warp;
+  const int col_blocks = (p.dv + cols - 1) / cols;
+  const int h = blockIdx.x / col_blocks, cb = blockIdx.x % col_blocks;
+  const int entry = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int r = lane / cols_per_warp;
+  const int col_local = warp * cols_per_warp + lane % cols_per_warp;
+  const int col = cb * cols + col_local;
+  const bool live = col < p.dv;
+  const int d = p.d, dv = p.dv, dp = DPT * rl;          // rows padded to dp >= d; the padding holds zeros
+  const int hqk = h / (p.H / p.Hqk);
+  const int t_begin = p.q_start[entry], t_end = p.q_start[entry + 1];
+  const int slot = p.slots[entry];
+  float* sbase = p.state + (static_cast<size_t>(slot) * p.H + h) * d * dv;
+
+  float S[DPT];
+#pragma unroll
+  for (int ii = 0; ii < DPT; ++ii) {
+    const int i = ii * rl + r;
+    S[ii] = (live && i < d) ? sbase[static_cast<size_t>(i) * dv + col] : 0.f;
+  }
+  float* ks = smem;                              // [chunk][dp]
+  float* qs = ks + kScanChunk * dp;              // [chunk][dp]
+  float* gs = qs + kScanChunk * dp;              // [chunk][dp] (gated only)
+  float* vs = gs + (GATED ? kScanChunk * dp : 0); // [chunk][cols]
+  float* bs = vs + kScanChunk * cols;            // [chunk]
+  const float dec = GATED ? 1.f : p.decay[h];
+  const T* qg = static_cast<const T*>(p.q);
+  const T* kg = static_cast<const T*>(p.k);
+  const T* vg = static_cast<const T*>(p.v);
+
+  for (int t0 = t_begin; t0 < t_end; t0 += kScanChunk) {
+    const int count = min(kScanChunk, t_end - t0);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < count * dp; idx += kScanThreads) {
+      const int tt = idx / dp, i = idx % dp;
+      const size_t row = static_cast<size_t>(t0 + tt);
+      float kv = 0.f, qv = 0.f, gv = 0.f;
+      if (i < d) {
+        kv = to_float(kg[row * p.ldk + hqk * d + i]);
+        qv = to_float(qg[row * p.ldq + hqk * d + i]);
+        if (p.act) { kv = silu_f(kv); qv = silu_f(qv); }
+        if (GATED) gv = p.gate[row * p.ldg + h * d + i];
+      }
+      ks[idx] = kv;
+      qs[idx] = qv;
+      if (GATED) gs[idx] = gv;
+    }
+    for (int idx = threadIdx.x; idx < count * cols; idx += kScanThreads) {
+      const int tt = idx / cols, c = cb * cols + idx % cols;
+      float vv = 0.f;
+      if (c < dv) {
+        vv = to_float(vg[static_cast<size_t>(t0 + tt) * p.ldv + h * dv + c]);
+        if (p.act) vv = silu_f(vv);
+      }
+      vs[idx] = vv;
+    }
+    if (DELTA && threadIdx.x < count) bs[threadIdx.x] = p.beta[static_cast<size_t>(t0 + threadIdx.x) * p.ldb + h];
+    __syncthreads();
+    for (int tt = 0; tt < count; ++tt) {
+      const float* kt = ks + tt * dp;
+      const float* qt = qs + tt * dp;
+      const float* gt = gs + tt * dp;
+      float dot[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int ii = 0; ii < DPT; ++ii) {
+        const int i = ii * rl + r;
+        S[ii] *= GATED ? gt[i] : dec;
+        if (DELTA) dot[ii & 3] = fmaf(S[ii], kt[i], dot[ii & 3]);
+      }
+      float u = vs[tt * cols + col_local];
+      if (DELTA) {
+        float sum = (dot[0] + dot[1]) + (dot[2] + dot[3]);
+        for (int o = cols_per_warp; o < 32; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        u = bs[tt] * (u - sum);
+      }
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int ii = 0; ii < DPT; ++ii) {
+        const int i = ii * rl + r;
+        S[ii] = fmaf(kt[i], u, S[ii]);
+        acc[ii & 3] = fmaf(S[ii], qt[i], acc[ii & 3]);
+      }
+      float o_sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+      for (int o = cols_per_warp; o < 32; o <<= 1) o_sum += __shfl_xor_sync(0xffffffffu, o_sum, o);
+      if (live && r == 0) p.out[static_cast<size_t>(t0 + tt) * p.ldo + h * dv + col] = o_sum;
+    }
+  }
+#pragma unroll
+  for (int ii = 0; ii < DPT; ++ii) {
+    const int i = ii * rl + r;
+    if (live && i < d) sbase[static_cast<size_t>(i) * dv + col] = S[ii];
+  }
+}
+
+template <typename T, bool DELTA, bool GATED>
+int launch_scan(const ScanParams& p, int entries, cudaStream_t stream) {
+  const int dpt = (p.d + p.rl - 1) / p.rl;
+  const int cols = (kScanThreads / 32) * (32 / p.rl);
+  dim3 grid(p.H * ((p.dv + cols - 1) / cols), entries);
+  if (grid.y > 65535) return B200_ERR_TOO_LARGE;
+  const int dpt8 = (dpt + 7) / 8 * 8;
+  const size_t smem = sizeof(float) * (static_cast<size_t>(kScanChunk) * dpt8 * p.rl * (GATED ? 3 : 2) + kScanChunk * cols + kScanChunk);
+  if (smem > 48 * 1024) return B200_ERR_TOO_LARGE;
+  switch (dpt8) {
+    case 8: launch(linear_scan_kernel<T, 8, DELTA, GATED>, grid, dim3(kScanThreads), smem, stream, p); break;
+    case 16: launch(linear_scan_kernel<T, 16, DELTA, GATED>, grid, dim3(kScanThreads), smem, stream, p); break;
+    case 24: launch(linear_scan_kernel<T, 24, DELTA, GATED>, grid, dim3(kScanThreads), smem, stream, p); break;
+    case 32: launch(linear_scan_kernel<T, 32, DELTA, GATED>, grid, dim3(kScanThreads), smem, stream, p); break;
+    default: return B200_ERR_TOO_LARGE;
+  }
+  return launch_status();
+}
+
+// ---------------------------------------------- preparation of a gated delta rule's inputs
+struct DeltaPrepareParams {
+  const void* proj; int ld;        // [n, ld] stacked projection: q | k | v | beta | decay rank | ...
+  int b_off, a_off, rank;          // columns of the beta logits and of the low-rank decay input
+  const float* taps; int ntaps;    // [C, ntaps], C = 2 G d + H dv channels in the order q, k, v
+  const float* conv_state;         // [slots, ntaps - 1, C]: inputs of the positions before this step, oldest first
+  const float* a_log;              // [H]
+  const float* dt_bias;            // [H d]
+  const void* a_up;                // [H d, rank] storage type
+  float* q; float* k; float* v; float* g; float* beta;   // [n, G d], [n, G d], [n, H dv], [n, H d], [n, H]
+  const int* q_start; const int* slots; const int* token_entry;
+  int H, G, d, dv;
+  float unit_eps, q_scale;
+};
+
+// One CTA per token: convolution and SiLU of every channel, unit norm of each q and k head, the
+// decay factors g = exp(-exp(a_log) * softplus(low-rank(x) + dt_bias)), and beta = sigmoid(.).
+template <typename T>
+__global__ void __launch_bounds__(256) delta_prepare_kernel(const DeltaPrepareParams p) {
+  extern __shared__ float smem[];
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int entry = p.token_entry[t];
+  const int first = p.q_start[entry];
+  const int local = t - first;
+  const int slot = p.slots[entry];
+  const int qk = p.G * p.d, C = 2 * qk + p.H * p.dv, K = p.ntaps;
+  const T* proj = static_cast<const T*>(p.proj);
+  float* sc = smem;            // [C] channels after convolution and SiLU
+  float* low = smem + C;       // [rank]
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < K; ++j) {
+      const int back = K - 1 - j, at = local - back;
+      const float x = at >= 0 ? to_float(proj[static_cast<size_t>(first + at) * p.ld + c])
+                              : p.conv_state[(static_cast<size_t>(slot) * (K - 1) + (K - 1 + at)) * C + c];
+      acc = fmaf(p.taps[static_cast<size_t>(c) * K + j], x, acc);
+    }
+    sc[c] = silu_f(acc);
+  }
+  for (int i = threadIdx.x; i < p.rank; i += blockDim.x) low[i] = to_float(proj[static_cast<size_t>(t) * p.ld + p.a_off + i]);
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int head = warp; head < 2 * p.G; head += nwarps) {      // q heads, then k heads
+    const float* x = sc + head * p.d;
+    float ss = 0.f;
+    for (int i = lane; i < p.d; i += 32) ss = fmaf(x[i], x[i], ss);
+    ss = warp_sum(ss);
+    const bool is_q = head < p.G;
+    const float f = rsqrtf(ss + p.unit_eps) * (is_q ? p.q_scale : 1.f);
+    float* dst = (is_q ? p.q : p.k) + static_cast<size_t>(t) * qk + (is_q ? head : head - p.G) * p.d;
+    for (int i = lane; i < p.d; i += 32) dst[i] = x[i] * f;
+  }
+  const int hv = p.H * p.dv, hd = p.H * p.d;
+  for (int i = threadIdx.x; i < hv; i += blockDim.x) p.v[static_cast<size_t>(t) * hv + i] = sc[2 * qk + i];
+  for (int h = threadIdx.x; h < p.H; h += blockDim.x)
+    p.beta[static_cast<size_t>(t) * p.H + h] = sigmoid_f(to_float(proj[static_cast<size_t>(t) * p.ld + p.b_off + h]));
+  const T* up = static_cast<const T*>(p.a_up);
+  for (int i = threadIdx.x; i < hd; i += blockDim.x) {
+    float a = 0.f;
+    for (int j = 0; j < p.rank; ++j) a = fmaf(to_float(up[static_cast<size_t>(i) * p.rank + j]), low[j], a);
+    const float rate = expf(p.a_log[i / p.d]);
+    p.g[static_cast<size_t>(t) * hd + i] = expf(-rate * softplus_f(a + p.dt_bias[i]));
+  }
+}
+
+// After a step: the last taps-1 inputs of each request, from the step's rows and, where the step
+// was shorter than that, from what the state held.  One thread per channel walks the rows oldest
+// first; row s is written after row len + s (> s) has been read, so nothing is read after it changed.
+template <typename T>
+__global__ void conv_state_update_kernel(const T* __restrict__ proj, int ld, float* __restrict__ conv_state, int C, int ntaps,
+                                         const int* __restrict__ q_start, const int* __restrict__ slots) {
+  pdl_trigger();
+  pdl_wait();
+  const int entry = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int first = q_start[entry], len = q_start[entry + 1] - first;
+  float* st = conv_state + static_cast<size_t>(slots[entry]) * (ntaps - 1) * C;
+  for (int s = 0; s < ntaps - 1; ++s) {
+    const int at = len - (ntaps - 1) + s;
+    st[static_cast<size_t>(s) * C + c] = at >= 0 ? to_float(proj[static_cast<size_t>(first + at) * ld + c])
+                                                 : st[static_cast<size_t>(len + s) * C + c];
+  }
+}
+
+// ------------------------------------------------------------- group norm times sigmoid gate
+// out[t, c] = x[t, c] * rsqrt(mean over c's group of x^2 + eps) * w[c % group] * sigmoid(gate[t, c]);
+// the gate's logits are read from `gate_in` directly (rank 0) or formed as gate_up[c, :] . gate_in[t, :rank].
+template <typename T>
+__global__ void group_norm_gate_kernel(const float* __restrict__ x, int width, int group, const float* __restrict__ w, float eps,
+                                       const T* __restrict__ gate_in, int gate_ld, int rank, const T* __restrict__ gate_up,
+                                       T* __restrict__ out) {
+  __shared__ float scratch[32];
+  extern __shared__ float low[];
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x, base = blockIdx.y * group;
+  const float* row = x + static_cast<size_t>(t) * width + base;
+  for (int j = threadIdx.x; j < rank; j += blockDim.x) low[j] = to_float(gate_in[static_cast<size_t>(t) * gate_ld + j]);
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < group; i += blockDim.x) ss = fmaf(row[i], row[i], ss);
+  const float f = rsqrtf(block_sum(ss, scratch) / static_cast<float>(group) + eps);
+  for (int i = threadIdx.x; i < group; i += blockDim.x) {
+    const int c = base + i;
+    float logit;
+    if (rank == 0) {
+      logit = to_float(gate_in[static_cast<size_t>(t) * gate_ld + c]);
+    } else {
+      logit = 0.f;
+      for (int j = 0; j < rank; ++j) logit = fmaf(to_float(gate_up[static_cast<size_t>(c) * rank + j]), low[j], logit);
+    }
+    out[static_cast<size_t>(t) * width + c] = from_float<T>(row[i] * f * w[i] * sigmoid_f(logit));
+  }
+}
+
+}  // namespace b200
+
+// q, k: [n, Hqk * d] rows (strides ldq, ldk), v: [n, H * dv]; element type by `dtype`.  gate (float32 [n, H * d]) selects
+// per-row factors, else `decay` ([H]) is used; beta (float32 [n, H]) selects the delta rule.  state float32 [slots, H, d, dv].
+extern "C" int b200_linear_scan(const void* q, const void* k, const void* v, int ldq, int ldk, int ldv, const float* gate, int ldg,
+                                const float* decay, const float* beta, int ldb, float* state, float* out, int ldo,
+                                const int* q_start, const int* slots, int entries, int H, int Hqk, int d, int dv, int act,
+                                int dtype, cudaStream_t stream) {
+  using namespace b200;
+  if (entries <= 0) return 0;
+  if (H <= 0 || Hqk <= 0 || H % Hqk != 0 || d <= 0 || dv <= 0 || d > 256) return B200_ERR_BAD_SIZE;
+  if ((gate == nullptr) == (decay == nullptr)) return B200_ERR_BAD_SIZE;
+  ScanParams p{q, k, v, ldq, ldk, ldv, gate, ldg, decay, beta, ldb, state, out, ldo, q_start, slots, H, Hqk, d, dv, act, 1};
+  while (p.rl < 32 && (d + p.rl - 1) / p.rl > 32) p.rl *= 2;
+  while (p.rl < 4 && (d + p.rl - 1) / p.rl > 8) p.rl *= 2;
+  const bool delta = beta != nullptr, gated = gate != nullptr;
+  if (delta && gated) {
+    B200_DISPATCH_DTYPE(dtype, T, return (launch_scan<T, true, true>(p, entries, stream)));
+  } else if (!delta && !gated) {
+    B200_DISPATCH_DTYPE(dtype, T, return (launch_scan<T, false, false>(p, entries, stream)));
+  } else if (delta) {
+    B200_DISPATCH_DTYPE(dtype, T, return (launch_scan<T, true, false>(p, entries, stream)));
+  } else {
+    B200_DISPATCH_DTYPE(dtype, T, return (launch_scan<T, false, true>(p, entries, stream)));
+  }
+  return 0;
+}
+
+extern "C" int b200_delta_prepare(const void* proj, int ld, int b_off, int a_off, int rank, const float* taps, int ntaps,
+                                  const float* conv_state, const float* a_log, const float* dt_bias, const void* a_up,
+                                  float* q, float* k, float* v, float* g, float* beta, const int* q_start, const int* slots,
+                                  const int* token_entry, int n, int H, int G, int d, int dv, float unit_eps, float q_scale,
+                                  int dtype, cudaStream_t stream) {
+  using namespace b200;
+  if (n <= 0) return 0;
+  if (H <= 0 || G <= 0 || H % G != 0 || d <= 0 || dv <= 0 || ntaps <= 0 || rank < 0) return B200_ERR_BAD_SIZE;
+  DeltaPrepareParams p{proj, ld, b_off, a_off, rank, taps, ntaps, conv_state, a_log, dt_bias, a_up, q, k, v, g, beta,
+                       q_start, slots, token_entry, H, G, d, dv, unit_eps, q_scale};
+  const size_t smem = sizeof(float) * (static_cast<size_t>(2) * G * d + static_cast<size_t>(H) * dv + rank);
+  static DeviceOnce once_f32, once_bf16;
+  if (smem > 200 * 1024) return B200_ERR_TOO_LARGE;
+  if (dtype == kF32) {
+    if (int e = configure_once(once_f32, delta_prepare_kernel<float>, smem > 48 * 1024 ? 200 * 1024 : 0)) return e;
+    launch(delta_prepare_kernel<float>, dim3(n), dim3(256), smem, stream, p);
+  } else if (dtype == kBF16) {
+    if (int e = configure_once(once_bf16, delta_prepare_kernel<__nv_bfloat16>, smem > 48 * 1024 ? 200 * 1024 : 0)) return e;
+    launch(delta_prepare_kernel<__nv_bfloat16>, dim3(n), dim3(256), smem, stream, p);
+  } else {
+    return B200_ERR_BAD_DTYPE;
+  }
+  return launch_status();
+}
+
+extern "C" int b200_conv_state_update(const void* proj, int ld, float* conv_state, int C, int ntaps, const int* q_start,
+                                      const int* slots, int entries, int dtype, cudaStream_t stream) {
+  using namespace b200;
+  if (entries <= 0 || ntaps <= 1 || C <= 0) return 0;
+  dim3 grid((C + 127) / 128, entries);
+  if (grid.y > 65535) return B200_ERR_TOO_LARGE;
+  B200_DISPATCH_DTYPE(dtype, T, launch(conv_state_update_kernel<T>, grid, dim3(128), 0, stream, static_cast<const T*>(proj), ld,
+                                       conv_state, C, ntaps, q_start, slots));
+  return launch_status();
+}
+
+extern "C" int b200_group_norm_gate(const float* x, int n, int width, int group, const float* w, float eps, const void* gate_in,
+                                    int gate_ld, int rank, const void* gate_up, void* out, int dtype, cudaStream_t stream) {
+  using namespace b200;
+  if (n <= 0) return 0;
+  if (width <= 0 || group <= 0 || width % group != 0 || rank < 0 || rank > 4096) return B200_ERR_BAD_SIZE;
+  dim3 grid(n, width / group);
+  if (grid.y > 65535) return B200_ERR_TOO_LARGE;
+  const int threads = group >= 256 ? 256 : (group + 31) / 32 * 32;
+  B200_DISPATCH_DTYPE(dtype, T, launch(group_norm_gate_kernel<T>, grid, dim3(threads), sizeof(float) * rank, stream, x, width, group,
+                                       w, eps, static_cast<const T*>(gate_in), gate_ld, rank, static_cast<const T*>(gate_up),
+                                       static_cast<T*>(out)));
+  return launch_status();
+}

@@ -26,7 +26,7 @@ from ..errors import GenerationError
 from .runtime import LoadedModel, load
 from .step import StepEntry, StepRunner
 
-DEFAULT_LIVE_REQUESTS = 16
+DEFAULT_LIVE_REQUESTS = 4
 
 
 class TraceReplayer:

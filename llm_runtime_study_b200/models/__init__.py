@@ -1,4 +1,4 @@
-from . import qwen3  # registers the architecture
+from . import qwen3, sorulix  # registers the architectures
 from .description import LayerDescription, ModelDescription, tensor_schema
 from .loading import load_model_dir, random_model
 from .model import DecoderModel

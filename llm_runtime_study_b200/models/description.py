@@ -5,16 +5,20 @@ generic ``DecoderModel`` is built from it; the tensor schema, the cache groups
 and the random-weights mode are derived from it.  The order in which layers run
 is a list too: it may name a layer twice (weights shared between depths; each
 run of a layer has a cache of its own), and a run may instead use the cache that
-an earlier run writes (``cache_of``).
+an earlier run writes (``cache_of``).  ``before_run`` attaches a stream step to a
+run: something done to the residual rows right before that run's layer (what a
+pass over shared layers adds at its start).  ``stored_name`` maps the name a part
+gives a tensor to the name the checkpoint stores it under, where the two differ.
 """
 
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Mapping
+from typing import Any, Callable, Mapping
 
 from ..parts import embedding as _embedding_kinds  # noqa: F401  (registers the embedding and head kinds of this package)
-from ..parts.base import BLOCKS, EMBEDDINGS, HEADS, NORMS
+from ..parts import stream_steps as _stream_step_kinds  # noqa: F401  (registers the stream step kinds of this package)
+from ..parts.base import BLOCKS, EMBEDDINGS, HEADS, NORMS, STREAM_STEPS
 from ..weights.checkpoint import TensorSpec
 
 
@@ -42,11 +46,15 @@ class ModelDescription:
     head: Mapping[str, Any]               # output head description ("kind", default "linear_head") + "prefix"
     cache_of: tuple[int | None, ...] = () # per run: the earlier run whose cache it uses (None: its own)
     extra: Mapping[str, Any] = field(default_factory=dict)
+    before_run: Mapping[int, Mapping[str, Any]] = field(default_factory=dict)   # run -> stream step description + "prefix"
+    stored_name: Callable[[str], str] | None = None   # a part's tensor name -> the checkpoint's
 
     def __post_init__(self) -> None:
         n = len(self.layers)
         if not self.order or any(not 0 <= i < n for i in self.order):
             raise ValueError(f"layer order {self.order} does not index {n} layers")
+        if any(not 0 <= run < len(self.order) for run in self.before_run):
+            raise ValueError(f"stream steps are attached to runs {sorted(self.before_run)}, but there are {len(self.order)} runs")
         if not self.cache_of:
             object.__setattr__(self, "cache_of", (None,) * len(self.order))
         if len(self.cache_of) != len(self.order):
@@ -72,15 +80,32 @@ def build_parts(description: ModelDescription):
         "blocks": [(layer.prefix, BLOCKS.build(layer.block)) for layer in description.layers],
         "final_norm": (norm_prefix, NORMS.build(norm_params)),
         "head": (head_prefix, HEADS.build({"kind": "linear_head", **head_params})),
+        "stream_steps": {run: (_split(step)[0], STREAM_STEPS.build(_split(step)[1])) for run, step in description.before_run.items()},
     }
+
+
+def named_parts(parts) -> list:
+    """(prefix, part) of everything that owns tensors."""
+
+    return [parts["embedding"], *parts["blocks"], *parts["stream_steps"].values(), parts["final_norm"], parts["head"]]
+
+
+def join_schemas(named, stored_name: Callable[[str], str] | None) -> dict[str, TensorSpec]:
+    """The parts' tensors by the names the checkpoint stores them under.  Two parts may name the same
+    tensor (one table read by several steps); they must agree on it."""
+
+    schema: dict[str, TensorSpec] = {}
+    for prefix, part in named:
+        for name, spec in part.tensor_specs().items():
+            full = f"{prefix}.{name}"
+            full = stored_name(full) if stored_name is not None else full
+            if full in schema and schema[full] != spec:
+                raise ValueError(f"two parts describe the tensor {full!r} differently")
+            schema[full] = spec
+    return schema
 
 
 def tensor_schema(description: ModelDescription) -> dict[str, TensorSpec]:
     """Every tensor the checkpoint must (or may) hold, by its full name."""
 
-    parts = build_parts(description)
-    schema: dict[str, TensorSpec] = {}
-    for prefix, part in (parts["embedding"], *parts["blocks"], parts["final_norm"], parts["head"]):
-        for name, spec in part.tensor_specs().items():
-            schema[f"{prefix}.{name}"] = spec
-    return schema
+    return join_schemas(named_parts(build_parts(description)), description.stored_name)

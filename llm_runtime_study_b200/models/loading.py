@@ -26,8 +26,12 @@ def load_model_dir(model_dir: str | Path, runtime: Runtime, *, strict_dtype: boo
     off, any floating storage type is taken and converted."""
 
     arch, config = load_config(model_dir)
-    model = DecoderModel(arch.describe(config))
     checkpoint = Checkpoint.from_model_dir(model_dir)
+    if arch.describe_for_checkpoint is not None:
+        description = arch.describe_for_checkpoint(config, {info.name: info.shape for info in checkpoint.manifest})
+    else:
+        description = arch.describe(config)
+    model = DecoderModel(description)
     validate_manifest(checkpoint, model.tensor_schema(), architecture=arch.model_type,
                       torch_dtype=getattr(config, "torch_dtype", None) if strict_dtype else None)
     model.load(checkpoint.view(), runtime)

@@ -12,7 +12,7 @@ from ..cache.manager import CacheLayout, CacheManager, LayerCache
 from ..parts.base import ResidualStream, Runtime
 from ..weights.checkpoint import TensorSpec
 from ..weights.view import TensorView
-from .description import ModelDescription, build_parts
+from .description import ModelDescription, build_parts, join_schemas, named_parts
 
 
 class DecoderModel:
@@ -23,19 +23,15 @@ class DecoderModel:
         self.blocks = parts["blocks"]  # [(prefix, block)]
         self.final_norm_prefix, self.final_norm = parts["final_norm"]
         self.head_prefix, self.head = parts["head"]
+        self.stream_steps = parts["stream_steps"]    # run -> (prefix, step)
+        self._parts = parts
         self.order = description.order
         self.runtime: Runtime | None = None
         self._layer_caches: list[LayerCache] | None = None
 
     # ------------------------------------------------------------ weights
     def tensor_schema(self) -> dict[str, TensorSpec]:
-        schema: dict[str, TensorSpec] = {}
-        named = [(self.embedding_prefix, self.embedding), *self.blocks,
-                 (self.final_norm_prefix, self.final_norm), (self.head_prefix, self.head)]
-        for prefix, part in named:
-            for name, spec in part.tensor_specs().items():
-                schema[f"{prefix}.{name}"] = spec
-        return schema
+        return join_schemas(named_parts(self._parts), self.description.stored_name)
 
     def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
         """Place every weight.  ``tensors`` is keyed by checkpoint name and has
@@ -43,9 +39,13 @@ class DecoderModel:
 
         self.runtime = runtime
         view = TensorView.of(tensors)
+        if self.description.stored_name is not None:
+            view = view.renamed(self.description.stored_name)
         self.embedding.load(view.sub(self.embedding_prefix), runtime)
         for prefix, block in self.blocks:
             block.load(view.sub(prefix), runtime)
+        for prefix, step in self.stream_steps.values():
+            step.load(view.sub(prefix), runtime)
         self.final_norm.load(view.sub(self.final_norm_prefix), runtime)
         self.head.load(view.sub(self.head_prefix), runtime, embedding=self.embedding)
 
@@ -68,7 +68,8 @@ class DecoderModel:
     def graph_safe(self) -> bool:
         """Whether every part allows its launches to be replayed from a CUDA graph."""
 
-        parts = [self.embedding, *(block for _, block in self.blocks), self.final_norm, self.head]
+        parts = [self.embedding, *(block for _, block in self.blocks), *(step for _, step in self.stream_steps.values()),
+                 self.final_norm, self.head]
         return all(part.capture_safe() for part in parts)
 
     # ------------------------------------------------------------ forward
@@ -79,15 +80,26 @@ class DecoderModel:
         blocks = [self.blocks[index][1] for index in self.order]
         # the norm that reads the stream after each block: the next block's first norm, at last the final norm
         readers = [block.first_norm() for block in blocks[1:]] + [self.final_norm]
+        steps = self.stream_steps
+        for run in steps:       # a stream step changes the rows before the norm reads them: nothing is prepared for it
+            if run > 0:
+                readers[run - 1] = None
         if getattr(self.embedding, "fuses_norms", False):
-            first = self.embedding.forward(ctx.token_ids, next_norm=blocks[0].first_norm())
+            first = self.embedding.forward(ctx.token_ids, next_norm=None if 0 in steps else blocks[0].first_norm())
         else:
             first = self.embedding.forward(ctx.token_ids)
         if isinstance(first, tuple):     # (rows, the same rows prepared for the first norm)
             stream = ResidualStream(first[0], weighted=first[1], weighted_for=blocks[0].first_norm())
         else:
             stream = ResidualStream(first)
+        # the residual rows are updated in place; a step that reads the embedding's output gets a copy of it
+        first_rows = stream.resid.clone() if any(step.reads_first_rows for _, step in steps.values()) else None
         for run, (block, reader) in enumerate(zip(blocks, readers)):
+            if run in steps:
+                if stream.delta is not None:
+                    stream.resid += stream.delta
+                stream.put(None, None)
+                steps[run][1].forward(stream, ctx, first_rows)
             if block.fuses_norms:
                 block.forward(stream, ctx, self._layer_caches[run], next_norm=reader)
             else:

@@ -171,3 +171,112 @@ def paged_attention_simt(
          ptr(token_entry), ptr(block_table), block_table.shape[1], page_size, n, nq, nkv, d,
          float(scale), int(window), tag(q.dtype), stream_ptr())
     return out
+
+
+def qk_rownorm_write(
+    qkv: torch.Tensor, *, num_q_heads: int, num_kv_heads: int, head_dim: int, value_dim: int,
+    q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, eps: float, temp_coef: float, temp_every: int,
+    positions: torch.Tensor, token_entry: torch.Tensor, block_table: torch.Tensor, page_size: int,
+    k_pool: torch.Tensor, v_pool: torch.Tensor,
+) -> torch.Tensor:
+    """Rows ``[q | k | v]``: RMS norm of q and of k over the whole projection (all heads at once, weights of that
+    width), q times the position's temperature ``1 + coef * ln(floor((p + 1) / every) + 1)`` (``every = 0``: none);
+    q is returned as ``[N, nq, d]``, k and v are written into the pages ``[pages, nkv, page_size, d | dv]``."""
+
+    require(qkv, "qkv", dims=2)
+    n, width = qkv.shape
+    qw, kw = num_q_heads * head_dim, num_kv_heads * head_dim
+    if width < qw + kw + num_kv_heads * value_dim:
+        raise KernelError(f"qkv width {width} is less than nq*d + nkv*(d + dv)")
+    dt = qkv.dtype
+    require(positions, "positions", dtype=torch.int32, shape=(n,))
+    require(token_entry, "token_entry", dtype=torch.int32, shape=(n,))
+    require(block_table, "block_table", dtype=torch.int32, dims=2)
+    if q_weight is not None:
+        require(q_weight, "q_weight", dtype=torch.float32, shape=(qw,))
+    if k_weight is not None:
+        require(k_weight, "k_weight", dtype=torch.float32, shape=(kw,))
+    require(k_pool, "k_pool", dtype=dt, dims=4)
+    require(v_pool, "v_pool", dtype=dt, dims=4)
+    if tuple(k_pool.shape[1:]) != (num_kv_heads, page_size, head_dim) or tuple(v_pool.shape[1:]) != (num_kv_heads, page_size, value_dim):
+        raise KernelError(f"pools have shapes {tuple(k_pool.shape)} and {tuple(v_pool.shape)}, expected "
+                          f"[pages, {num_kv_heads}, {page_size}, {head_dim} | {value_dim}]")
+    q_out = torch.empty((n, num_q_heads, head_dim), dtype=dt, device=qkv.device)
+    call("b200_qk_rownorm_write", ptr(qkv), width, ptr(q_out), ptr(q_weight), ptr(k_weight), float(eps), float(temp_coef),
+         int(temp_every), ptr(positions), ptr(token_entry), ptr(block_table), block_table.shape[1], page_size, ptr(k_pool),
+         ptr(v_pool), n, num_q_heads, num_kv_heads, head_dim, value_dim, tag(dt), stream_ptr())
+    return q_out
+
+
+def paged_attention_simt_rules(
+    q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, *, positions: torch.Tensor, token_entry: torch.Tensor,
+    block_table: torch.Tensor, scale: float, window: int = 0, softcap: float = 0.0, slopes: torch.Tensor | None = None,
+    sink: bool = False,
+) -> torch.Tensor:
+    """``paged_attention_simt`` with rules on the scores: ``S <- cap * tanh(S / cap)`` (``softcap > 0``), then
+    ``S <- S - slopes[head] * (p - t)``, and with ``sink`` the weights ``exp(S) / (1 + sum exp(S))``.  Values may
+    have a head size of their own: q ``[N, nq, d]``, keys ``[pages, nkv, page, d]``, values ``[pages, nkv, page, dv]``,
+    result ``[N, nq, dv]``."""
+
+    require(q, "q", dims=3)
+    n, nq, d = q.shape
+    require(k_pool, "k_pool", dtype=q.dtype, dims=4)
+    require(v_pool, "v_pool", dtype=q.dtype, dims=4)
+    _, nkv, page_size, dk = k_pool.shape
+    dv = v_pool.shape[3]
+    if dk != d or tuple(v_pool.shape[:3]) != tuple(k_pool.shape[:3]):
+        raise KernelError(f"q head size {d}, key pool {tuple(k_pool.shape)} and value pool {tuple(v_pool.shape)} do not fit")
+    if d % 8:
+        raise KernelError(f"head size {d} is not a multiple of 8")
+    require(positions, "positions", dtype=torch.int32, shape=(n,))
+    require(token_entry, "token_entry", dtype=torch.int32, shape=(n,))
+    require(block_table, "block_table", dtype=torch.int32, dims=2)
+    if slopes is not None:
+        require(slopes, "slopes", dtype=torch.float32, shape=(nq,))
+    out = torch.empty((n, nq, dv), dtype=q.dtype, device=q.device)
+    call("b200_paged_attention_simt_rules", ptr(q), ptr(k_pool), ptr(v_pool), ptr(out), ptr(positions), ptr(token_entry),
+         ptr(block_table), block_table.shape[1], page_size, n, nq, nkv, d, dv, float(scale), int(window), float(softcap),
+         ptr(slopes), 1 if sink else 0, tag(q.dtype), stream_ptr())
+    return out
+
+
+def glu_limit(gate_up: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
+    """Rows ``[gate | up]``: ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``, ``g * sigmoid(alpha g) * (u + 1)``."""
+
+    require(gate_up, "gate_up", dims=2)
+    n, two_i = gate_up.shape
+    if two_i % 2:
+        raise KernelError("glu_limit: row width must be even ([gate | up])")
+    out = torch.empty((n, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    call("b200_glu_limit", ptr(gate_up), ptr(out), n, two_i // 2, float(limit), float(alpha), tag(gate_up.dtype), stream_ptr())
+    return out
+
+
+def rmsnorm_accumulate(x: torch.Tensor, weight: torch.Tensor, eps: float, factor: float, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``out (+)= factor * rms_norm(x) * weight`` on float32 rows; a fresh ``out`` is made (and not read) when none is given."""
+
+    require(x, "x", dtype=torch.float32, dims=2)
+    n, hidden = x.shape
+    require(weight, "weight", dtype=torch.float32, shape=(hidden,))
+    accumulate = out is not None
+    if out is None:
+        out = torch.empty_like(x)
+    else:
+        require(out, "out", dtype=torch.float32, shape=x.shape)
+    call("b200_rmsnorm_accumulate", ptr(x), ptr(weight), ptr(out), n, hidden, float(eps), float(factor), 1 if accumulate else 0,
+         stream_ptr())
+    return out
+
+
+def add_rows(resid: torch.Tensor, a: torch.Tensor | None = None, b: torch.Tensor | None = None,
+             vector: torch.Tensor | None = None) -> None:
+    """``resid += a + b + vector`` in place on float32 rows (each term optional; ``vector`` is one row for all)."""
+
+    require(resid, "resid", dtype=torch.float32, dims=2)
+    n, hidden = resid.shape
+    for t, name in ((a, "a"), (b, "b")):
+        if t is not None:
+            require(t, name, dtype=torch.float32, shape=resid.shape)
+    if vector is not None:
+        require(vector, "vector", dtype=torch.float32, shape=(hidden,))
+    call("b200_add_rows", ptr(resid), ptr(a), ptr(b), ptr(vector), n, hidden, stream_ptr())

@@ -44,6 +44,13 @@ _LIBRARIES = {
                 c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_void_p, c_void_p,
                 c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
             ],
+            "b200_qk_rownorm_write": [
+                c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_float, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+            ],
+            "b200_glu_limit": [c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_int, c_void_p],
+            "b200_rmsnorm_accumulate": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_int, c_void_p],
+            "b200_add_rows": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
         },
     ),
     "b200_gemm_f32": (
@@ -57,6 +64,27 @@ _LIBRARIES = {
                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                 c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,
             ],
+            "b200_paged_attention_simt_rules": [
+                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_int, c_int, c_void_p,
+            ],
+        },
+    ),
+    "b200_sequence_state": (
+        ("sequence_state.cu",),
+        {
+            "b200_linear_scan": [
+                c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p,
+                c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+            ],
+            "b200_delta_prepare": [
+                c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p,
+            ],
+            "b200_conv_state_update": [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
+            "b200_group_norm_gate": [c_void_p, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p,
+                                     c_void_p, c_int, c_void_p],
         },
     ),
 }

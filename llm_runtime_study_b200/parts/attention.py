@@ -8,10 +8,11 @@ from typing import Any, Mapping
 import torch
 
 from ..ops import attention_bf16
+from ..ops import attention_rules
 from ..ops import functional as F
 from ..weights.checkpoint import TensorSpec
 from ..weights.view import TensorView
-from .base import MIXERS, NORMS, POSITION_ENCODINGS, Mixer, PagedKV, Runtime
+from .base import MIXERS, NORMS, POSITION_ENCODINGS, Mixer, PagedKV, PagedTensors, Runtime
 from .linear import Projection
 from .norm import RMSNorm
 
@@ -142,3 +143,96 @@ class GroupedQueryAttention(Mixer):
         )
         out = ctx.attention(q, cache, scale=self.scale, window=self.window or 0)
         return self.o_proj(out.view(out.shape[0], -1), torch.float32, add_to=residual, next_norm=next_norm)
+
+
+@MIXERS.register("sink_attention")
+class SinkAttention(Mixer):
+    """Grouped-query causal attention without rotation, with rules on the scores instead, every one a
+    parameter:
+
+    * q and k are RMS-normalised over the *whole* projection (all heads at once, a weight of that width),
+      before they are split into heads (``qk_norm_eps``; ``None``: no norm);
+    * q is multiplied by the position's temperature ``1 + coef * ln(floor((p + 1) / every) + 1)``
+      (``temperature = (coef, every)``);
+    * ``S = scale * q.k``; ``S <- softcap * tanh(S / softcap)``; ``S <- S - slope_h * (i - j)`` with
+      ``slope_h = 2^(-slope_exponent * (h + 1) / heads)`` for head ``h`` (``slope_exponent = None``: no bias);
+    * ``sink``: the weights are ``exp(S_j) / (1 + sum exp(S))``, a key of score 0 that has no value.
+
+    Keys have ``head_dim`` columns, values ``value_dim``.  Tensors: ``q``, ``k``, ``v`` (one stacked product),
+    ``q.norm``, ``k.norm``, ``o``.  Positions enter through the temperature and the distance only, so the
+    cache holds k and v as they leave the norm.
+    """
+
+    graph_safe = True
+
+    def __init__(
+        self, *, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int | None = None,
+        scale: float | None = None, qk_norm_eps: float | None = None, temperature: tuple[float, int] | None = None,
+        softcap: float | None = None, slope_exponent: float | None = None, sink: bool = False, window: int | None = None,
+    ) -> None:
+        value_dim = head_dim if value_dim is None else value_dim
+        if min(hidden_size, num_heads, num_kv_heads, head_dim, value_dim) <= 0:
+            raise ValueError("attention sizes must be positive")
+        if num_heads % num_kv_heads:
+            raise ValueError(f"num_heads {num_heads} is not a multiple of num_kv_heads {num_kv_heads}")
+        if head_dim % 8 or head_dim > 256 or value_dim > 256:
+            raise ValueError(f"head_dim {head_dim} must be a multiple of 8, and both head sizes at most 256: no kernel takes others")
+        if temperature is not None and int(temperature[1]) <= 0:
+            raise ValueError("the temperature's period must be positive")
+        if softcap is not None and softcap <= 0:
+            raise ValueError("softcap must be positive")
+        self.hidden_size, self.num_heads, self.num_kv_heads = hidden_size, num_heads, num_kv_heads
+        self.head_dim, self.value_dim = head_dim, value_dim
+        self.scale = 1.0 / math.sqrt(head_dim) if scale is None else float(scale)
+        self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
+        self.temperature = None if temperature is None else (float(temperature[0]), int(temperature[1]))
+        self.softcap = None if softcap is None else float(softcap)
+        self.slope_exponent = None if slope_exponent is None else float(slope_exponent)
+        self.sink, self.window = bool(sink), window
+
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        q_out, k_out, v_out, h = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim, self.num_kv_heads * self.value_dim, self.hidden_size
+        specs = {
+            "q": TensorSpec((q_out, h)), "k": TensorSpec((k_out, h)), "v": TensorSpec((v_out, h)),
+            "o": TensorSpec((h, self.num_heads * self.value_dim)),
+        }
+        if self.qk_norm_eps is not None:
+            specs["q.norm"] = TensorSpec((q_out,), init="one_plus_normal", std=0.05)
+            specs["k.norm"] = TensorSpec((k_out,), init="one_plus_normal", std=0.05)
+        return specs
+
+    def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
+        self.runtime = runtime
+        self.qkv_proj = Projection([tensors["q"], tensors["k"], tensors["v"]], None, runtime)
+        self.o_proj = Projection([tensors["o"]], None, runtime)
+        self.q_weight = self.k_weight = None
+        if self.qk_norm_eps is not None:
+            self.q_weight = runtime.place_vector_f32(tensors["q.norm"])
+            self.k_weight = runtime.place_vector_f32(tensors["k.norm"])
+        self.slopes = None
+        if self.slope_exponent is not None:
+            # formed in float64, kept in float32
+            slopes = [2.0 ** (-self.slope_exponent * (h + 1) / self.num_heads) for h in range(self.num_heads)]
+            self.slopes = torch.tensor(slopes, dtype=torch.float64).to(torch.float32).to(runtime.device)
+
+    def cache_requirement(self) -> PagedTensors:
+        return PagedTensors(
+            tensors=(("keys", (self.num_kv_heads, self.head_dim)), ("values", (self.num_kv_heads, self.value_dim))),
+            window=self.window,
+        )
+
+    def forward(self, x: torch.Tensor, ctx: Any, cache: Any) -> torch.Tensor:
+        qkv = self.qkv_proj(x)
+        table = ctx.block_table(cache.group)
+        coef, every = self.temperature or (0.0, 0)
+        q = F.qk_rownorm_write(
+            qkv, num_q_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim, value_dim=self.value_dim,
+            q_weight=self.q_weight, k_weight=self.k_weight, eps=self.qk_norm_eps or 0.0, temp_coef=coef, temp_every=every,
+            positions=ctx.positions, token_entry=ctx.token_entry, block_table=table, page_size=cache.page_size,
+            k_pool=cache.keys, v_pool=cache.values,
+        )
+        out = attention_rules.paged_attention_rules(
+            q, cache, ctx, table, scale=self.scale, window=self.window or 0, softcap=self.softcap or 0.0,
+            slopes=self.slopes, sink=self.sink,
+        )
+        return self.o_proj(out.view(out.shape[0], -1), torch.float32)

@@ -18,11 +18,13 @@ Interfaces (all tensors live on the CUDA device; ``x`` is ``[tokens, width]``):
                     fused rotate-and-write kernel, or ``None``; then
                     ``apply(q, k, ctx)`` is called on ``[tokens, heads, d]`` instead.
 ``Mixer``           ``cache_requirement()`` says what per-request memory it needs
-                    (``PagedKV``, ``FixedState`` or ``None``);
+                    (``PagedTensors``/``PagedKV``, ``FixedState``, a tuple of these, or ``None``);
                     ``forward(x, ctx, cache) -> float32 [tokens, hidden]``.
 ``FeedForward``     ``forward(x, ctx) -> float32 [tokens, hidden]``.
 ``Block``           ``forward(stream, ctx, cache)`` where ``stream`` carries the
                     residual rows and the not-yet-added output of the previous part.
+``StreamStep``      ``forward(stream, ctx, first_rows)``: something done to the residual
+                    rows between two runs of layers (``first_rows``: the embedding's output).
 Embeddings (``forward(token_ids) -> float32 [tokens, hidden]``) and output heads
 (``forward(x) -> float32 [rows, vocab]``; ``load`` also gets ``embedding=`` for tied
 weights) are registered kinds too.
@@ -94,10 +96,12 @@ class PagedKV(PagedTensors):
 @dataclass(frozen=True)
 class FixedState:
     """Per-request state of fixed size: one array ``[slots, *shape]`` per layer,
-    zeroed when a request takes a slot."""
+    zeroed when a request takes a slot.  A mixer that keeps several such arrays
+    returns a tuple of them and tells them apart by ``name``."""
 
     shape: tuple[int, ...]
     dtype: torch.dtype = torch.float32
+    name: str = "state"
 
 
 # ------------------------------------------------------------------ parts
@@ -161,7 +165,10 @@ class Mixer(Part):
     # residual rows it may return ``WeightedRows`` prepared for that norm instead of ``None``.
     fuses_norms = False
 
-    def cache_requirement(self) -> PagedKV | FixedState | None:
+    def cache_requirement(self) -> "PagedTensors | FixedState | tuple | None":
+        """What the mixer keeps per request: pages (at most one requirement of that kind), arrays of fixed
+        size (any number, told apart by their names), a tuple of both, or nothing."""
+
         return None
 
     def forward(self, x: torch.Tensor, ctx: Any, cache: Any) -> torch.Tensor:
@@ -189,6 +196,15 @@ class Block(Part):
         return None
 
     def forward(self, stream: "ResidualStream", ctx: Any, cache: Any) -> None:
+        raise NotImplementedError
+
+
+class StreamStep(Part):
+    """Something done to the residual rows between two runs of layers (before the run it is attached to):
+    rows added at the start of a pass over shared layers, for instance.  It gets the stream with everything
+    before it added in (``stream.delta`` is ``None``) and the embedding's output rows."""
+
+    def forward(self, stream: "ResidualStream", ctx: Any, first_rows: torch.Tensor) -> None:
         raise NotImplementedError
 
 
@@ -279,3 +295,4 @@ POSITION_ENCODINGS = Registry("position encoding")
 MIXERS = Registry("mixer")
 FEED_FORWARDS = Registry("feed-forward")
 BLOCKS = Registry("block")
+STREAM_STEPS = Registry("stream step")

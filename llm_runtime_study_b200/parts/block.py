@@ -23,30 +23,31 @@ class PreNormBlock(Block):
     """``h = h + mixer(norm_1(h)); h = h + ffn(norm_2(h))``
     (mini_llm/model/qwen.py:58-72).  The additions are carried out by the *next*
     norm, in float32, while it reads the rows anyway.  ``names`` gives the
-    checkpoint's name of each sub-part below the layer's prefix."""
+    checkpoint's name of each sub-part below the layer's prefix.  A layer
+    without a feed-forward (``feed_forward=None``) is its first half only."""
 
     def __init__(
-        self, *, mixer: Mapping[str, Any], feed_forward: Mapping[str, Any], mixer_norm: Mapping[str, Any],
-        ffn_norm: Mapping[str, Any], names: Mapping[str, str] | None = None,
+        self, *, mixer: Mapping[str, Any], feed_forward: Mapping[str, Any] | None, mixer_norm: Mapping[str, Any],
+        ffn_norm: Mapping[str, Any] | None = None, names: Mapping[str, str] | None = None,
     ) -> None:
         self.names = {**_DEFAULT_NAMES, **(names or {})}
         self.mixer = MIXERS.build(mixer)
-        self.feed_forward = FEED_FORWARDS.build(feed_forward)
         self.mixer_norm = NORMS.build(mixer_norm)
-        self.ffn_norm = NORMS.build(ffn_norm)
+        self.feed_forward = FEED_FORWARDS.build(feed_forward) if feed_forward else None
+        self.ffn_norm = NORMS.build(ffn_norm) if feed_forward else None
+        if feed_forward and not ffn_norm:
+            raise ValueError("a pre_norm block with a feed-forward needs the norm before it (ffn_norm)")
 
     graph_safe = True
 
     def children(self):
-        return (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward)
+        return tuple(part for _, part in self._parts())
 
     def _parts(self):
-        return (
-            (self.names["mixer_norm"], self.mixer_norm),
-            (self.names["mixer"], self.mixer),
-            (self.names["ffn_norm"], self.ffn_norm),
-            (self.names["feed_forward"], self.feed_forward),
-        )
+        parts = [(self.names["mixer_norm"], self.mixer_norm), (self.names["mixer"], self.mixer)]
+        if self.feed_forward is not None:
+            parts += [(self.names["ffn_norm"], self.ffn_norm), (self.names["feed_forward"], self.feed_forward)]
+        return tuple(parts)
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
         return {f"{prefix}.{n}": s for prefix, part in self._parts() for n, s in part.tensor_specs().items()}
@@ -64,7 +65,10 @@ class PreNormBlock(Block):
 
     def forward(self, stream: ResidualStream, ctx: Any, cache: Any, next_norm: Any = None) -> None:
         x = stream.take_rows(self.mixer_norm, self.mixer)
-        stream.put(self._run(self.mixer, (x, ctx, cache), stream.resid, self.ffn_norm), self.ffn_norm)
+        after_mixer = self.ffn_norm if self.feed_forward is not None else next_norm
+        stream.put(self._run(self.mixer, (x, ctx, cache), stream.resid, after_mixer), after_mixer)
+        if self.feed_forward is None:
+            return
         x = stream.take_rows(self.ffn_norm, self.feed_forward)
         stream.put(self._run(self.feed_forward, (x, ctx), stream.resid, next_norm), next_norm)
 

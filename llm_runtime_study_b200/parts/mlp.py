@@ -56,3 +56,35 @@ class SwiGLU(FeedForward):
     def forward(self, x: Any, ctx: Any, residual: torch.Tensor | None = None, next_norm: Any = None):
         hidden = self.gate_up_proj.swiglu(x) if self.interleaved else F.silu_mul(self.gate_up_proj(x))
         return self.down_proj(hidden, torch.float32, add_to=residual, next_norm=next_norm)
+
+
+@FEED_FORWARDS.register("limited_glu")
+class LimitedGLU(FeedForward):
+    """``g = min(W_gate x + b_gate, limit)``, ``u = clamp(W_up x + b_up, -limit, limit)``,
+    ``y = g * sigmoid(alpha g) * (u + 1)``, output ``W_down y + b_down``.  gate and up are one stacked
+    product.  Tensors: ``gate``, ``gate.b``, ``up``, ``up.b``, ``down``, ``down.b``."""
+
+    graph_safe = True
+
+    def __init__(self, *, hidden_size: int, intermediate_size: int, limit: float, alpha: float = 1.702) -> None:
+        if hidden_size <= 0 or intermediate_size <= 0 or limit <= 0:
+            raise ValueError("limited_glu sizes and its limit must be positive")
+        self.hidden_size, self.intermediate_size, self.limit, self.alpha = hidden_size, intermediate_size, float(limit), float(alpha)
+
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        h, i = self.hidden_size, self.intermediate_size
+        return {
+            "gate": TensorSpec((i, h)), "gate.b": TensorSpec((i,)), "up": TensorSpec((i, h)), "up.b": TensorSpec((i,)),
+            "down": TensorSpec((h, i)), "down.b": TensorSpec((h,)),
+        }
+
+    def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
+        self.runtime = runtime
+        self.gate_up_proj = Projection([tensors["gate"], tensors["up"]], [tensors["gate.b"], tensors["up.b"]], runtime)
+        self.down_proj = Projection([tensors["down"]], [tensors["down.b"]], runtime)
+
+    adds_to_residual = True
+
+    def forward(self, x: Any, ctx: Any, residual: torch.Tensor | None = None):
+        hidden = F.glu_limit(self.gate_up_proj(x), self.limit, self.alpha)
+        return self.down_proj(hidden, torch.float32, add_to=residual)

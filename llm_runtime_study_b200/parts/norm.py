@@ -15,22 +15,28 @@ from .base import NORMS, Norm, Runtime
 class RMSNorm(Norm):
     """``y = w * x * rsqrt(mean(x^2) + eps)``: statistics in float32, the weight
     applied as ``w`` (mini_llm/nn/norm.py:42-46).  Random weights are
-    ``1 + N(0, 0.05)``."""
+    ``1 + N(0, 0.05)``.  With ``offset`` the stored weight lies around zero and the
+    factor is ``offset + w`` (formed once, in float32, when the weight is placed);
+    random weights are then ``N(0, 0.05)``."""
 
     graph_safe = True
 
-    def __init__(self, dim: int, eps: float) -> None:
+    def __init__(self, dim: int, eps: float, offset: float = 0.0) -> None:
         if dim <= 0 or eps <= 0:
             raise ValueError(f"rms_norm needs dim > 0 and eps > 0, got {dim}, {eps}")
-        self.dim, self.eps = dim, float(eps)
+        self.dim, self.eps, self.offset = dim, float(eps), float(offset)
         self.weight: torch.Tensor | None = None
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
+        if self.offset:
+            return {"weight": TensorSpec((self.dim,), init="normal", std=0.05)}
         return {"weight": TensorSpec((self.dim,), init="one_plus_normal", std=0.05)}
 
     def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
         self.runtime = runtime
         self.weight = runtime.place_vector_f32(tensors["weight"])
+        if self.offset:
+            self.weight += self.offset
 
     def fusable(self) -> tuple[torch.Tensor, float]:
         return self.weight, self.eps

@@ -14,6 +14,11 @@
 // t <= p (and t > p - window with a window), P = softmax(S), o = P.v; query head j reads KV
 // head j / (nq / nkv).  Scores, maxima, exponentials, sums and the output accumulate in
 // float32; P is rounded to bfloat16 for the P.V product, as the operands of Q.K^T are.
+//
+// The prefill kernel and the decode kernel with the query heads on the row side exist a second
+// time with rules on the scores (template RULES): S <- cap * tanh(S / cap), S <- S - slope_h * (p - t)
+// with one slope per query head, and a sink (a key of score 0 without a value, so that the
+// denominator of the softmax gains a 1).  The kernels without rules are unchanged by this.
 #include "common.cuh"
 #include "mma.cuh"
 
@@ -44,6 +49,10 @@ struct AttnParams {
   int nq, nkv, group, gs, slices;  // group = nq / nkv; gs = heads of a group per CTA; slices = ceil(group / gs)
   float scale_log2;
   int window;
+  // rules on the scores (the RULES kernels only)
+  float scale, softcap;            // softcap <= 0: none
+  const float* slopes;             // [nq] or null
+  int sink;
   // prefill
   const int* tile_entry;
   const int* tile_start;
@@ -94,12 +103,22 @@ __device__ __forceinline__ float quad_sum(float v) {
 
 // One warp: NT8 tiles of 8 keys (rows key0.. of the shared tile) against its 16 query rows.
 // Updates the running maximum m, the per-thread partial sum l and the output o.
-template <int NT8>
+struct ScoreRules {
+  float scale, softcap, inv_cap;   // scores in natural units: S * scale, then the cap
+  float slope[2];                  // of the two rows' query heads
+  int pos[2];                      // the two rows' positions (the distance to key t is pos - t)
+};
+
+__device__ __forceinline__ float tanh_exp(float y) {   // 1 - 2 / (e^(2y) + 1): two special-function results
+  return 1.f - __fdividef(2.f, __expf(2.f * y) + 1.f);
+}
+
+template <int NT8, bool RULES = false>
 __device__ __forceinline__ void warp_attend(const bf16* kbuf, const bf16* vbuf, int key0, int t_first,
                                             const uint32_t (&qf)[KSTEPS][4], const bool (&row_ok)[2],
                                             const int (&row_hi)[2], const int (&row_lo)[2],
                                             float scale_log2, float (&m)[2], float (&l)[2],
-                                            float (&o)[DTILES][4]) {
+                                            float (&o)[DTILES][4], const ScoreRules* rules = nullptr) {
   const int lane = threadIdx.x & 31, tig = lane & 3;
   float s[NT8][4];
 #pragma unroll
@@ -124,7 +143,14 @@ __device__ __forceinline__ void warp_attend(const bf16* kbuf, const bf16* vbuf, 
       const int i = e >> 1;
       const int t = t_first + key0 + nt * 8 + tig * 2 + (e & 1);
       const bool visible = row_ok[i] && t <= row_hi[i] && t >= row_lo[i];
-      s[nt][e] = visible ? s[nt][e] * scale_log2 : -INFINITY;
+      if constexpr (RULES) {
+        float x = s[nt][e] * rules->scale;
+        if (rules->softcap > 0.f) x = rules->softcap * tanh_exp(x * rules->inv_cap);
+        x -= rules->slope[i] * static_cast<float>(rules->pos[i] - t);
+        s[nt][e] = visible ? x * 1.4426950408889634f : -INFINITY;
+      } else {
+        s[nt][e] = visible ? s[nt][e] * scale_log2 : -INFINITY;
+      }
       mx[i] = fmaxf(mx[i], s[nt][e]);
     }
   }
@@ -183,7 +209,7 @@ __device__ __forceinline__ void load_q_fragments(uint32_t (&qf)[KSTEPS][4], cons
 }
 
 // ------------------------------------------------------------------ prefill / mixed batches
-template <int WARPS>
+template <int WARPS, bool RULES = false>
 __global__ void __launch_bounds__(WARPS * 32) prefill_attention_kernel(AttnParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* ks = reinterpret_cast<bf16*>(smem_raw);
@@ -209,6 +235,19 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_kernel(AttnParam
     row_hi[i] = p_first + tl;
     row_lo[i] = p.window > 0 ? max(0, row_hi[i] - p.window + 1) : 0;
     row_off[i] = (static_cast<long>(tok0 + tl) * p.nq + kvh * p.group + g) * D;
+  }
+  ScoreRules rules{};
+  if constexpr (RULES) {
+    rules.scale = p.scale;
+    rules.softcap = p.softcap;
+    rules.inv_cap = p.softcap > 0.f ? 1.f / p.softcap : 0.f;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int R = warp * 16 + gid + i * 8;
+      const int g = slice * p.gs + R % p.gs;
+      rules.slope[i] = (p.slopes && g < p.group) ? p.slopes[kvh * p.group + g] : 0.f;
+      rules.pos[i] = row_hi[i];
+    }
   }
   uint32_t qf[KSTEPS][4];
   load_q_fragments(qf, p.q, row_off, row_ok);
@@ -236,14 +275,15 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_kernel(AttnParam
       cp_async_wait<0>();
     }
     __syncthreads();
-    warp_attend<BN / 8>(ks + buf * BN * LDS, vs + buf * BN * LDS, 0, t_begin + j * BN, qf, row_ok, row_hi, row_lo,
-                        p.scale_log2, m, l, o);
+    warp_attend<BN / 8, RULES>(ks + buf * BN * LDS, vs + buf * BN * LDS, 0, t_begin + j * BN, qf, row_ok, row_hi, row_lo,
+                               p.scale_log2, m, l, o, &rules);
     __syncthreads();
   }
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     if (!row_ok[i]) continue;
-    const float total = quad_sum(l[i]);
+    float total = quad_sum(l[i]);
+    if (RULES && p.sink) total += exp2f(-m[i]);     // the sink's exp(0 - maximum); no visible key: infinity, a row of zeros
     const float inv = total > 0.f ? 1.f / total : 0.f;
     bf16* dst = p.out + row_off[i];
 #pragma unroll
@@ -254,6 +294,7 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_kernel(AttnParam
 
 // --------------------------------------------------------------------------- decode
 // grid (splits, nkv * slices, requests); 4 warps, each takes 16 keys of every 64-key tile.
+template <bool RULES = false>
 __global__ void __launch_bounds__(128) decode_attention_kernel(AttnParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* ks = reinterpret_cast<bf16*>(smem_raw);
@@ -282,6 +323,18 @@ __global__ void __launch_bounds__(128) decode_attention_kernel(AttnParams p) {
     row_hi[i] = len - 1;
     row_lo[i] = lo;
     row_off[i] = (static_cast<long>(b) * p.nq + kvh * p.group + g) * D;
+  }
+  ScoreRules rules{};
+  if constexpr (RULES) {
+    rules.scale = p.scale;
+    rules.softcap = p.softcap;
+    rules.inv_cap = p.softcap > 0.f ? 1.f / p.softcap : 0.f;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int g = slice * p.gs + gid + i * 8;
+      rules.slope[i] = (p.slopes && row_ok[i]) ? p.slopes[kvh * p.group + g] : 0.f;
+      rules.pos[i] = len - 1;
+    }
   }
   uint32_t qf[KSTEPS][4];
   load_q_fragments(qf, p.q, row_off, row_ok);
@@ -339,8 +392,8 @@ __global__ void __launch_bounds__(128) decode_attention_kernel(AttnParams p) {
       cp_async_wait<0>();
     }
     __syncwarp();
-    warp_attend<2>(wk + buf * WB * LDS, wv + buf * WB * LDS, 0, c0 + block * WB, qf, row_ok, hi_here, row_lo,
-                   p.scale_log2, m, l, o);
+    warp_attend<2, RULES>(wk + buf * WB * LDS, wv + buf * WB * LDS, 0, c0 + block * WB, qf, row_ok, hi_here, row_lo,
+                          p.scale_log2, m, l, o, &rules);
     __syncwarp();
   }
   __syncthreads();
@@ -381,6 +434,7 @@ __global__ void __launch_bounds__(128) decode_attention_kernel(AttnParams p) {
     }
     const int head = kvh * p.group + g;
     if (p.num_splits == 1) {
+      if (RULES && p.sink) L += exp2f(-base);
       p.out[(static_cast<long>(b) * p.nq + head) * D + col] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
     } else {
       const long slot = (static_cast<long>(b) * p.nq + head) * p.num_splits + split;
@@ -606,7 +660,7 @@ __global__ void __launch_bounds__(128) decode_attention_t_kernel(AttnParams p) {
 
 // grid (nq, requests), D threads: combine the splits of one (request, head)
 __global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                    bf16* __restrict__ out, int nq, int num_splits) {
+                                    bf16* __restrict__ out, int nq, int num_splits, int sink) {
   pdl_trigger();
   pdl_wait();
   const long base = (static_cast<long>(blockIdx.y) * nq + blockIdx.x) * num_splits;
@@ -620,6 +674,7 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_o, const floa
       acc += part_o[(base + s) * D + col] * f;
       L += part_ml[(base + s) * 2 + 1] * f;
     }
+    if (sink) L += exp2f(-ref);      // the sink's exp(0 - maximum), once for all parts
     out[(static_cast<long>(blockIdx.y) * nq + blockIdx.x) * D + col] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
   }
 }
@@ -662,23 +717,52 @@ extern "C" int b200_attention_head_dim() { return HEAD_DIM; }
 // tokens_per_tile = rows / heads_per_cta consecutive tokens.
 extern "C" int b200_attention_prefill_rows() { return 64; }
 
-extern "C" int b200_attention_prefill_bf16(const void* q, const void* k_pool, const void* v_pool, void* out,
-                                           const int* positions, const int* block_table, int table_stride,
-                                           int page_size, int nq, int nkv, float scale, int window,
-                                           const int* tile_entry, const int* tile_start, const int* tile_count,
-                                           int num_tiles, cudaStream_t stream) {
+static int prefill_entry(bool with_rules, const void* q, const void* k_pool, const void* v_pool, void* out,
+                         const int* positions, const int* block_table, int table_stride,
+                         int page_size, int nq, int nkv, float scale, int window, float softcap, const float* slopes, int sink,
+                         const int* tile_entry, const int* tile_start, const int* tile_count,
+                         int num_tiles, cudaStream_t stream) {
   if (num_tiles <= 0) return 0;
   AttnParams p{};
   if (int e = fill_common(p, q, k_pool, v_pool, out, positions, block_table, table_stride, page_size, nq, nkv, scale, window)) return e;
   p.tile_entry = tile_entry;
   p.tile_start = tile_start;
   p.tile_count = tile_count;
-  static DeviceOnce once;
-  if (int e = configure_once(once, prefill_attention_kernel<4>, kSmemBytes)) return e;
+  p.scale = scale;
+  p.softcap = softcap;
+  p.slopes = slopes;
+  p.sink = sink;
   dim3 grid(nkv * p.slices, num_tiles);
   if (grid.y > 65535) return B200_ERR_TOO_LARGE;
-  launch(prefill_attention_kernel<4>, dim3(grid), dim3(128), kSmemBytes, stream, p);
+  if (with_rules) {
+    static DeviceOnce once_rules;
+    if (int e = configure_once(once_rules, prefill_attention_kernel<4, true>, kSmemBytes)) return e;
+    launch(prefill_attention_kernel<4, true>, dim3(grid), dim3(128), kSmemBytes, stream, p);
+  } else {
+    static DeviceOnce once;
+    if (int e = configure_once(once, prefill_attention_kernel<4>, kSmemBytes)) return e;
+    launch(prefill_attention_kernel<4>, dim3(grid), dim3(128), kSmemBytes, stream, p);
+  }
   return launch_status();
+}
+
+extern "C" int b200_attention_prefill_bf16(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                           const int* positions, const int* block_table, int table_stride,
+                                           int page_size, int nq, int nkv, float scale, int window,
+                                           const int* tile_entry, const int* tile_start, const int* tile_count,
+                                           int num_tiles, cudaStream_t stream) {
+  return prefill_entry(false, q, k_pool, v_pool, out, positions, block_table, table_stride, page_size, nq, nkv, scale, window,
+                       0.f, nullptr, 0, tile_entry, tile_start, tile_count, num_tiles, stream);
+}
+
+// The same with rules on the scores: softcap (<= 0: none), slopes ([nq] floats or null), sink (0 or 1).
+extern "C" int b200_attention_prefill_rules_bf16(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                                 const int* positions, const int* block_table, int table_stride,
+                                                 int page_size, int nq, int nkv, float scale, int window, float softcap,
+                                                 const float* slopes, int sink, const int* tile_entry, const int* tile_start,
+                                                 const int* tile_count, int num_tiles, cudaStream_t stream) {
+  return prefill_entry(true, q, k_pool, v_pool, out, positions, block_table, table_stride, page_size, nq, nkv, scale, window,
+                       softcap, slopes, sink, tile_entry, tile_start, tile_count, num_tiles, stream);
 }
 
 extern "C" long b200_attention_decode_scratch_floats(int requests, int nq, int num_splits) {
@@ -717,14 +801,46 @@ extern "C" int b200_attention_decode_bf16(const void* q, const void* k_pool, con
 #endif
   {
     static DeviceOnce once;
-    if (int e = configure_once(once, decode_attention_kernel, kSmemBytes)) return e;
+    if (int e = configure_once(once, decode_attention_kernel<false>, kSmemBytes)) return e;
     dim3 grid(num_splits, nkv * p.slices, requests);
-    launch(decode_attention_kernel, dim3(grid), dim3(128), kSmemBytes, stream, p);
+    launch(decode_attention_kernel<false>, dim3(grid), dim3(128), kSmemBytes, stream, p);
   }
   if (int e = launch_status()) return e;
   if (num_splits > 1) {
     dim3 mgrid(nq, requests);
-    launch(decode_merge_kernel, dim3(mgrid), dim3(kMergeThreads), 0, stream, p.part_o, p.part_ml, p.out, nq, num_splits);
+    launch(decode_merge_kernel, dim3(mgrid), dim3(kMergeThreads), 0, stream, p.part_o, p.part_ml, p.out, nq, num_splits, 0);
+  }
+  return launch_status();
+}
+
+// One query token per request with rules on the scores (see b200_attention_prefill_rules_bf16); the kernel with the
+// query heads on the row side, the parts merged with the sink added once.
+extern "C" int b200_attention_decode_rules_bf16(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                                const int* kv_len, const int* block_table, int table_stride,
+                                                int page_size, int requests, int nq, int nkv, float scale, int window,
+                                                float softcap, const float* slopes, int sink,
+                                                int num_splits, float* scratch, long scratch_floats, cudaStream_t stream) {
+  if (requests <= 0) return 0;
+  AttnParams p{};
+  if (int e = fill_common(p, q, k_pool, v_pool, out, nullptr, block_table, table_stride, page_size, nq, nkv, scale, window)) return e;
+  if (num_splits < 1 || requests > 65535) return B200_ERR_BAD_SIZE;
+  if (scratch_floats < b200_attention_decode_scratch_floats(requests, nq, num_splits)) return 10004;
+  p.kv_len = kv_len;
+  p.num_splits = num_splits;
+  p.part_o = scratch;
+  p.part_ml = scratch + static_cast<long>(requests) * nq * num_splits * D;
+  p.scale = scale;
+  p.softcap = softcap;
+  p.slopes = slopes;
+  p.sink = sink;
+  static DeviceOnce once;
+  if (int e = configure_once(once, decode_attention_kernel<true>, kSmemBytes)) return e;
+  dim3 grid(num_splits, nkv * p.slices, requests);
+  launch(decode_attention_kernel<true>, dim3(grid), dim3(128), kSmemBytes, stream, p);
+  if (int e = launch_status()) return e;
+  if (num_splits > 1) {
+    dim3 mgrid(nq, requests);
+    launch(decode_merge_kernel, dim3(mgrid), dim3(kMergeThreads), 0, stream, p.part_o, p.part_ml, p.out, nq, num_splits, sink);
   }
   return launch_status();
 }

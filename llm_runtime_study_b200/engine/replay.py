@@ -26,7 +26,8 @@ from ..errors import GenerationError
 from .runtime import LoadedModel, load
 from .step import StepEntry, StepRunner
 
-DEFAULT_LIVE_REQUESTS = 4
+DEFAULT_LIVE_REQUESTS = 16
+TRACE_RUN_LIVE_REQUESTS = 4     # what the command line gives a trace unless told otherwise
 
 
 class TraceReplayer:
@@ -99,7 +100,8 @@ def main(argv: list[str] | None = None) -> int:
     parser.add_argument("--max-tokens", type=int, required=True,
                         help="most tokens live requests hold at once (each rounded up to 64)")
     parser.add_argument("--page-size", type=int, default=16)
-    parser.add_argument("--max-requests", type=int, default=DEFAULT_LIVE_REQUESTS, help="most requests live at a time")
+    parser.add_argument("--max-requests", type=int, default=TRACE_RUN_LIVE_REQUESTS,
+                        help="request slots: most requests live at a time (slots and pages are used again as requests end)")
     parser.add_argument("--device", default="cuda:0")
     args = parser.parse_args(argv)
     print("[trace_run] loading model and kernels ...", file=sys.stderr, flush=True)

@@ -2,11 +2,23 @@
 
 from __future__ import annotations
 
+import os
 from typing import Any
 
 import torch
 
+from . import attention_bf16, native
 from . import functional as F
+
+# "mma": the tensor-core kernels wherever they take the shape; "simt": the CUDA-core kernel everywhere
+BACKEND = os.environ.get("LLM_RUNTIME_STUDY_B200_ATTENTION_RULES", "mma")
+
+
+def tensor_core_supported(q: torch.Tensor, cache: Any) -> bool:
+    """bfloat16, keys and values of one head size that the mma.sync kernels are built for."""
+
+    d = q.shape[2]
+    return (q.dtype == torch.bfloat16 and cache.values.shape[3] == d and attention_bf16.supported(d))
 
 
 def paged_attention_rules(q: torch.Tensor, cache: Any, ctx: Any, table: torch.Tensor, *, scale: float, window: int = 0,
@@ -14,9 +26,39 @@ def paged_attention_rules(q: torch.Tensor, cache: Any, ctx: Any, table: torch.Te
     """Causal attention of the batch's query tokens ``[N, heads, d]`` over their requests' pages with
     ``S <- cap * tanh(S / cap)``, ``S <- S - slope_h * distance`` and the sink's ``1 +`` in the denominator.
 
-    Both run types: the CUDA-core kernel (one warp per token and head, float32 arithmetic, tiles of 32 keys
-    from key 0, so the order of every sum depends on the token's position alone)."""
+    float32 runtime, and shapes no tensor-core kernel takes (values of another head size than the keys): the
+    CUDA-core kernel (one warp per token and head, float32 arithmetic, tiles of 32 keys from key 0, so the order
+    of every sum depends on the token's position alone).  bfloat16 runtime: the mma.sync kernels of the plain
+    attention, built a second time with the rules applied to the score tile (one for batches that hold prompt
+    portions, a split-sequence one with a merge for batches of single decoded tokens)."""
 
+    if BACKEND == "mma" and tensor_core_supported(q, cache):
+        n, nq, d = q.shape
+        keys, values = cache.keys, cache.values
+        _, _, _, nkv, page_size, gs, slices = attention_bf16._geometry(q, keys)
+        lib = attention_bf16.library_name(d)
+        out = torch.empty_like(q)
+        if ctx.all_decode and n == ctx.num_entries:
+            splits = attention_bf16.decode_splits(n, nkv, slices, ctx.max_kv_len, head_dim=d)
+            floats = native.query("b200_attention_decode_scratch_floats", n, nq, splits, library=lib)
+            scratch = torch.empty(max(floats, 1), dtype=torch.float32, device=q.device)
+            native.call(
+                "b200_attention_decode_rules_bf16", q.data_ptr(), keys.data_ptr(), values.data_ptr(), out.data_ptr(),
+                ctx.kv_len.data_ptr(), table.data_ptr(), table.shape[1], page_size, n, nq, nkv, float(scale), int(window),
+                float(softcap), native.ptr(slopes), 1 if sink else 0, splits, scratch.data_ptr(), floats, native.stream_ptr(),
+                library=lib, launches=2 if splits > 1 else 1)
+            return out
+        maps = ctx.__dict__.setdefault("_tile_maps", {})
+        per_tile = 64 // gs
+        if per_tile not in maps:
+            maps[per_tile] = attention_bf16.tile_map(ctx.q_lens, per_tile, q.device, ctx.kv_lens)
+        tiles, count = maps[per_tile]
+        native.call(
+            "b200_attention_prefill_rules_bf16", q.data_ptr(), keys.data_ptr(), values.data_ptr(), out.data_ptr(),
+            ctx.positions.data_ptr(), table.data_ptr(), table.shape[1], page_size, nq, nkv, float(scale), int(window),
+            float(softcap), native.ptr(slopes), 1 if sink else 0, tiles[0].data_ptr(), tiles[1].data_ptr(), tiles[2].data_ptr(),
+            count, native.stream_ptr(), library=lib)
+        return out
     return F.paged_attention_simt_rules(
         q, cache.keys, cache.values, positions=ctx.positions, token_entry=ctx.token_entry, block_table=table,
         scale=scale, window=window, softcap=softcap, slopes=slopes, sink=sink,

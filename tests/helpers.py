@@ -208,3 +208,64 @@ def pool_tokens(steps: list[dict]) -> int:
 
 def dump_trace(steps: list[dict]) -> str:
     return "".join(json.dumps(s) + "\n" for s in steps)
+
+
+# ----------------------------------------------------------------- Sorulix
+# Two small configurations that differ in every size and option.  A: a loop over layers 1..2 (three passes), a
+# layer without a feed-forward, grouped heads in both attention and delta rule, key and value sizes that differ,
+# a soft cap and a query temperature that both bite.  B: no loop, no soft cap, no temperature, one head here and
+# there, a period-2 convolution, sizes that are no multiples of 16.
+SORULIX_A = {
+    "architecture": "Sorulix", "vocab": 97, "width": 64, "norm": {"eps": 1e-5},
+    "loop": {"start": 1, "stop": 3, "times": 3},
+    "layers": [
+        {"type": "channel_delta", "mixer": {"heads": 4, "kv_heads": 2, "dim": 24, "vdim": 16, "conv": 3},
+         "mlp": {"kind": "dense", "ff": 80, "limit": 1.5}},
+        {"type": "parallel", "mixer": {
+            "left": {"heads": 4, "kv_heads": 2, "dim": 16, "vdim": 24, "scale": 0.9, "softcap": 1.0, "q_temp": {"coef": 0.5, "every": 3}},
+            "right": {"heads": 2, "dim": 8, "vdim": 40, "decay": [0.9, 0.5]}},
+         "mlp": {"kind": "dense", "ff": 80, "limit": 1.5}},
+        {"type": "channel_delta", "mixer": {"heads": 4, "kv_heads": 2, "dim": 24, "vdim": 16, "conv": 3}, "mlp": None},
+        {"type": "parallel", "mixer": {
+            "left": {"heads": 2, "kv_heads": 1, "dim": 32, "vdim": 32, "scale": 0.5, "softcap": 2.0, "q_temp": {"coef": 0.2, "every": 1}},
+            "right": {"heads": 3, "dim": 16, "vdim": 16, "decay": [0.99, 0.7, 0.2]}},
+         "mlp": {"kind": "dense", "ff": 48, "limit": 0.7}},
+    ],
+}
+SORULIX_A_RANKS = {0: (5, 7), 2: (8, 3)}
+SORULIX_B = {
+    "architecture": "Sorulix", "vocab": 131, "width": 48, "norm": {"eps": 1e-6},
+    "layers": [
+        {"type": "parallel", "mixer": {
+            "left": {"heads": 3, "kv_heads": 3, "dim": 8, "vdim": 8, "scale": 1.0},
+            "right": {"heads": 1, "dim": 40, "vdim": 8, "decay": [0.97]}},
+         "mlp": {"kind": "dense", "ff": 56, "limit": 0.7}},
+        {"type": "channel_delta", "mixer": {"heads": 2, "kv_heads": 2, "dim": 40, "vdim": 48, "conv": 2},
+         "mlp": {"kind": "dense", "ff": 56, "limit": 2.5}},
+    ],
+}
+SORULIX_B_RANKS = {1: (16, 1)}
+SORULIX = {"A": (SORULIX_A, SORULIX_A_RANKS, 11, 4), "B": (SORULIX_B, SORULIX_B_RANKS, 12, 16)}   # config, ranks, seed, page size
+
+
+def make_sorulix_dir(path: Path, config: dict, ranks: dict, seed: int, *, torch_dtype: str = "float32", gain: float = 8.0):
+    """Write a Sorulix model folder with random weights; return (path, {name: CPU tensor as stored}).  The matrices
+    are drawn ``gain`` times larger than the framework's default so that limits, caps and gates bite."""
+
+    from llm_runtime_study_b200.config import SorulixConfig
+    from llm_runtime_study_b200.models.description import tensor_schema
+    from llm_runtime_study_b200.models.sorulix import describe_sorulix
+    from llm_runtime_study_b200.weights.random_init import random_state
+    from llm_runtime_study_b200.weights.safetensors_io import write_file
+
+    schema = tensor_schema(describe_sorulix(SorulixConfig.from_dict(config), ranks))
+    dtype = {"float32": torch.float32, "bfloat16": torch.bfloat16}[torch_dtype]
+    state = random_state(schema, seed, dtype=torch.float32, include_optional=False)
+    for name, tensor in state.items():
+        if tensor.dim() == 2 and not name.endswith(".conv") and name not in ("loop.step",):
+            tensor *= gain
+    state = {name: tensor.to(dtype) for name, tensor in state.items()}
+    path.mkdir(parents=True, exist_ok=True)
+    (path / "config.json").write_text(json.dumps(config, indent=1), encoding="utf-8")
+    write_file(path / "model.safetensors", state)
+    return path, state

@@ -5,6 +5,12 @@ the engine.  It takes a ``config.json`` dict and ``{tensor name: tensor}`` with 
 checkpoint's own names.  ``dtype`` is the arithmetic type (float64 separates
 rounding from faults).
 
+``store`` (optional) is applied wherever a serving engine with 16-bit activations keeps a tensor in
+memory between two operations: normalised rows, the results of projections, q and k as they enter the
+attention, a mixer's gated read-out, the gated feed-forward rows.  With ``store=round_bfloat16`` the plain
+model carries those roundings; the residual stream, the statistics, the states and the logits stay in
+``dtype`` either way.
+
 Notation: ``T`` tokens at positions ``0..T-1``; ``rms(x) = x / sqrt(mean(x^2) + eps)``
 over the last axis; every linear map is ``x @ W.T`` with ``W`` stored ``[out, in]``.
 """
@@ -18,6 +24,16 @@ import torch
 
 
 # ----------------------------------------------------------------- elementary
+def keep(x: torch.Tensor) -> torch.Tensor:
+    return x
+
+
+def round_bfloat16(x: torch.Tensor) -> torch.Tensor:
+    """Round to the nearest bfloat16 and widen again."""
+
+    return x.to(torch.bfloat16).to(x.dtype)
+
+
 def rms(x: torch.Tensor, eps: float) -> torch.Tensor:
     return x / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + eps)
 
@@ -81,20 +97,21 @@ def sink_attention(q, k, v, *, scale: float, softcap: float | None, slopes: torc
     return out
 
 
-def left_mixer(h, w: Mapping[str, torch.Tensor], p: str, c: Mapping, eps: float) -> torch.Tensor:
+def left_mixer(h, w: Mapping[str, torch.Tensor], p: str, c: Mapping, eps: float, store=keep) -> torch.Tensor:
     """The softmax half of a parallel mixer; ``p`` is the prefix of its tensors."""
 
     T = h.shape[0]
     H, G, d, dv = c["heads"], c["kv_heads"], c["dim"], c["vdim"]
-    q = norm_plain(h @ w[f"{p}.q"].T, w[f"{p}.q.norm"], eps)       # over the whole projection, before the split
-    k = norm_plain(h @ w[f"{p}.k"].T, w[f"{p}.k.norm"], eps)
-    v = h @ w[f"{p}.v"].T
+    q = norm_plain(store(h @ w[f"{p}.q"].T), w[f"{p}.q.norm"], eps)       # over the whole projection, before the split
+    k = store(norm_plain(store(h @ w[f"{p}.k"].T), w[f"{p}.k.norm"], eps))
+    v = store(h @ w[f"{p}.v"].T)
     temp = c.get("q_temp")
     if temp:
         q = q * query_temperature(torch.arange(T), temp["coef"], temp["every"]).to(h.dtype)[:, None]
+    q = store(q)
     o = sink_attention(q.view(T, H, d), k.view(T, G, d), v.view(T, G, dv), scale=c["scale"],
                        softcap=c.get("softcap"), slopes=distance_slopes(H))
-    return o.reshape(T, H * dv) @ w[f"{p}.o"].T
+    return store(o).reshape(T, H * dv) @ w[f"{p}.o"].T
 
 
 # ------------------------------------------------------------- linear attention
@@ -110,22 +127,22 @@ def decayed_outer_sum(q, k, v, decay: torch.Tensor) -> torch.Tensor:
     return torch.stack(out)
 
 
-def right_mixer(h, w, p: str, c: Mapping, eps: float) -> torch.Tensor:
+def right_mixer(h, w, p: str, c: Mapping, eps: float, store=keep) -> torch.Tensor:
     T = h.shape[0]
     H, d, dv = c["heads"], c["dim"], c["vdim"]
-    q = silu(h @ w[f"{p}.q"].T).view(T, H, d)
-    k = silu(h @ w[f"{p}.k"].T).view(T, H, d)
-    v = silu(h @ w[f"{p}.v"].T).view(T, H, dv)
+    q = silu(store(h @ w[f"{p}.q"].T)).view(T, H, d)
+    k = silu(store(h @ w[f"{p}.k"].T)).view(T, H, d)
+    v = silu(store(h @ w[f"{p}.v"].T)).view(T, H, dv)
     o = decayed_outer_sum(q, k, v, torch.tensor(c["decay"], dtype=torch.float64)).reshape(T, H * dv)
-    o = norm_plain(o, w[f"{p}.norm"], eps) * sigmoid(h @ w[f"{p}.g"].T)
+    o = store(norm_plain(o, w[f"{p}.norm"], eps) * sigmoid(store(h @ w[f"{p}.g"].T)))
     return o @ w[f"{p}.o"].T
 
 
-def parallel_mixer(h, w, p: str, c: Mapping, eps: float) -> torch.Tensor:
+def parallel_mixer(h, w, p: str, c: Mapping, eps: float, store=keep) -> torch.Tensor:
     """Both halves read the same rows; each output is normalised over the model width; the mean of the two."""
 
-    left = norm_plain(left_mixer(h, w, f"{p}.left", c["left"], eps), w[f"{p}.left.out"], eps)
-    right = norm_plain(right_mixer(h, w, f"{p}.right", c["right"], eps), w[f"{p}.right.out"], eps)
+    left = norm_plain(left_mixer(h, w, f"{p}.left", c["left"], eps, store), w[f"{p}.left.out"], eps)
+    right = norm_plain(right_mixer(h, w, f"{p}.right", c["right"], eps, store), w[f"{p}.right.out"], eps)
     return 0.5 * (left + right)
 
 
@@ -161,32 +178,32 @@ def gated_delta_scan(q, k, v, beta, g) -> torch.Tensor:
     return torch.stack(out)
 
 
-def channel_delta_mixer(h, w, p: str, c: Mapping, eps: float) -> torch.Tensor:
+def channel_delta_mixer(h, w, p: str, c: Mapping, eps: float, store=keep) -> torch.Tensor:
     T = h.shape[0]
     H, G, d, dv = c["heads"], c["kv_heads"], c["dim"], c["vdim"]
-    q = silu(short_convolution(h @ w[f"{p}.q"].T, w[f"{p}.q.conv"])).view(T, G, d)
-    k = silu(short_convolution(h @ w[f"{p}.k"].T, w[f"{p}.k.conv"])).view(T, G, d)
-    v = silu(short_convolution(h @ w[f"{p}.v"].T, w[f"{p}.v.conv"])).view(T, H, dv)
+    q = silu(short_convolution(store(h @ w[f"{p}.q"].T), w[f"{p}.q.conv"])).view(T, G, d)
+    k = silu(short_convolution(store(h @ w[f"{p}.k"].T), w[f"{p}.k.conv"])).view(T, G, d)
+    v = silu(short_convolution(store(h @ w[f"{p}.v"].T), w[f"{p}.v.conv"])).view(T, H, dv)
     q = unit(q) * d ** -0.5
     k = unit(k)
     q = q.repeat_interleave(H // G, dim=1)
     k = k.repeat_interleave(H // G, dim=1)
-    beta = sigmoid(h @ w[f"{p}.b"].T)
+    beta = sigmoid(store(h @ w[f"{p}.b"].T))
     rate = torch.exp(w[f"{p}.A_log"])[None, :, None]
-    step = softplus((h @ w[f"{p}.a1"].T) @ w[f"{p}.a2"].T + w[f"{p}.dt_bias"]).view(T, H, d)
+    step = softplus(store(h @ w[f"{p}.a1"].T) @ w[f"{p}.a2"].T + w[f"{p}.dt_bias"]).view(T, H, d)
     g = torch.exp(-rate * step)
     o = gated_delta_scan(q, k, v, beta, g)                      # [T, H, dv]
     o = norm_plain(o, w[f"{p}.norm"], eps)
-    o = o * sigmoid((h @ w[f"{p}.g1"].T) @ w[f"{p}.g2"].T).view(T, H, dv)
+    o = store(o * sigmoid(store(h @ w[f"{p}.g1"].T) @ w[f"{p}.g2"].T).view(T, H, dv))
     return o.reshape(T, H * dv) @ w[f"{p}.o"].T
 
 
 # ---------------------------------------------------------------- feed-forward
-def limited_glu(h, w, p: str, c: Mapping) -> torch.Tensor:
+def limited_glu(h, w, p: str, c: Mapping, store=keep) -> torch.Tensor:
     limit = c["limit"]
-    g = torch.clamp(h @ w[f"{p}.gate"].T + w[f"{p}.gate.b"], max=limit)
-    u = torch.clamp(h @ w[f"{p}.up"].T + w[f"{p}.up.b"], min=-limit, max=limit)
-    y = g * sigmoid(1.702 * g) * (u + 1.0)
+    g = torch.clamp(store(h @ w[f"{p}.gate"].T + w[f"{p}.gate.b"]), max=limit)
+    u = torch.clamp(store(h @ w[f"{p}.up"].T + w[f"{p}.up.b"]), min=-limit, max=limit)
+    y = store(g * sigmoid(1.702 * g) * (u + 1.0))
     return y @ w[f"{p}.down"].T + w[f"{p}.down.b"]
 
 
@@ -206,7 +223,7 @@ def layer_runs(config: Mapping) -> list[tuple[int, int | None]]:
 
 
 def forward(weights: Mapping[str, torch.Tensor], config: Mapping, token_ids, dtype: torch.dtype = torch.float64,
-            *, layers_out: list | None = None) -> torch.Tensor:
+            *, layers_out: list | None = None, store=keep) -> torch.Tensor:
     """Logits ``[T, vocab]`` of one whole sequence."""
 
     w = {n: t.to(dtype) for n, t in weights.items()}
@@ -219,16 +236,16 @@ def forward(weights: Mapping[str, torch.Tensor], config: Mapping, token_ids, dty
                 x = x + first
             x = x + w["loop.step"][starts_pass]
         layer, p = config["layers"][index], f"l{index}"
-        h = norm_around_zero(x, w[f"{p}.norm1"], eps)
+        h = store(norm_around_zero(x, w[f"{p}.norm1"], eps))
         if layer["type"] == "parallel":
-            x = x + parallel_mixer(h, w, f"{p}.mix", layer["mixer"], eps)
+            x = x + parallel_mixer(h, w, f"{p}.mix", layer["mixer"], eps, store)
         elif layer["type"] == "channel_delta":
-            x = x + channel_delta_mixer(h, w, f"{p}.mix", layer["mixer"], eps)
+            x = x + channel_delta_mixer(h, w, f"{p}.mix", layer["mixer"], eps, store)
         else:
             raise ValueError(f"unknown layer type {layer['type']!r}")
         if layer.get("mlp"):
-            x = x + limited_glu(norm_around_zero(x, w[f"{p}.norm2"], eps), w, f"{p}.mlp", layer["mlp"])
+            x = x + limited_glu(store(norm_around_zero(x, w[f"{p}.norm2"], eps)), w, f"{p}.mlp", layer["mlp"], store)
         if layers_out is not None:
             layers_out.append(x.clone())
-    x = norm_around_zero(x, w["final.norm"], eps)
+    x = store(norm_around_zero(x, w["final.norm"], eps))
     return x @ w["embed"].T

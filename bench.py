@@ -538,6 +538,217 @@ def run_decode_32b(args) -> dict:
                        "page_size": PAGE_SIZE, "timing": "wall clock through the scheduler", "peaks": pk["source"]}}
 
 
+# ------------------------------------------------------------------------------ Sorulix beside Qwen3
+SORULIX_SIZES = {
+    # name: (width, feed-forward, heads, kv heads, head size, pairs of layers, vocabulary)
+    "2k": (2048, 8192, 16, 4, 128, 2, 32000),
+    "4k": (4096, 12288, 32, 8, 128, 2, 32000),
+}
+
+
+def _sorulix_config(width, ff, heads, kv_heads, d, pairs, vocab) -> dict:
+    parallel = {"type": "parallel", "mixer": {
+        "left": {"heads": heads, "kv_heads": kv_heads, "dim": d, "vdim": d, "scale": d ** -0.5, "softcap": 50.0,
+                 "q_temp": {"coef": 0.3, "every": 64}},
+        "right": {"heads": heads, "dim": d, "vdim": d, "decay": [1.0 - 2.0 ** (-5 - 3 * h / heads) for h in range(heads)]}},
+        "mlp": {"kind": "dense", "ff": ff, "limit": 7.0}}
+    delta = {"type": "channel_delta", "mixer": {"heads": heads, "kv_heads": heads, "dim": d, "vdim": d, "conv": 4},
+             "mlp": {"kind": "dense", "ff": ff, "limit": 7.0}}
+    return {"architecture": "Sorulix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "torch_dtype": "bfloat16",
+            "layers": [parallel, delta] * pairs}
+
+
+def _qwen3_like(width, ff, heads, kv_heads, d, pairs, vocab) -> dict:
+    cfg = dict(QWEN3_8B)
+    cfg.update(vocab_size=vocab, hidden_size=width, intermediate_size=ff, num_hidden_layers=2 * pairs, num_attention_heads=heads,
+               num_key_value_heads=kv_heads, head_dim=d, max_position_embeddings=16384, tie_word_embeddings=True,
+               bos_token_id=1, eos_token_id=2)
+    return cfg
+
+
+def run_sorulix(args) -> dict:
+    """Prefill and decode of Sorulix at layer sizes of real models (random weights), beside Qwen3 at equal width,
+    feed-forward, heads, head size and depth, through the same engine; then the new kernels alone, each against
+    the bytes or flops it must move, beside the kernel of the Qwen3 path that does the like work."""
+
+    import torch
+
+    from llm_runtime_study_b200.cache.slots import SlotRecord
+    from llm_runtime_study_b200.engine.engine import Engine
+    from llm_runtime_study_b200.engine.step import StepEntry
+    from llm_runtime_study_b200.ops import native
+
+    torch.cuda.set_device(0)
+    peak = peaks()
+    generator = torch.Generator().manual_seed(0)
+    greedy = SlotRecord(position=0)
+    context, prefill_tokens = CONTEXT, PREFILL_TOKENS
+
+    def timed(fn, repeat):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(repeat):
+            fn()
+        end.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(end) / repeat
+
+    def measure(cfg, vocab):
+        def ids(n):
+            return torch.randint(0, vocab, (n,), generator=generator).tolist()
+
+        batches = (1, 8, 32)
+        engine = Engine.from_random_weights(
+            cfg, seed=0, device="cuda:0", dtype="bfloat16", max_seq_len=8192, max_batch_size=max(batches), page_size=PAGE_SIZE,
+            max_cache_tokens=max(batches) * (context + args.steps + 64), max_tokens_per_step=prefill_tokens, use_cuda_graph=True)
+        runner, manager, sampler = engine.runner, engine.cache_manager, engine._sampler
+        prompt = ids(prefill_tokens)
+
+        def one_prefill():
+            request = manager.admit()
+            runner.step_sampled([StepEntry(request, prompt, [prefill_tokens - 1], greedy)], sampler).tokens()
+            manager.release(request)
+
+        for _ in range(3):
+            one_prefill()
+        out = {"prefill_tokens": prefill_tokens, "prefill_ms": round(statistics.median(timed(one_prefill, 1) for _ in range(5)), 3)}
+        out["prefill_tok_s"] = round(prefill_tokens / out["prefill_ms"] * 1e3)
+        for batch in batches:
+            requests = [manager.admit() for _ in range(batch)]
+            for request in requests:
+                runner.step_sampled([StepEntry(request, ids(context), [context - 1], greedy)], sampler)
+            handles = []
+            for _ in range(max(args.warmup, 3)):
+                handles.append(runner.decode_sampled(requests, sampler))
+            handles.pop().tokens()
+            before = native.launch_count()
+            ms = timed(lambda: handles.append(runner.decode_sampled(requests, sampler)), args.steps)
+            out[f"decode_b{batch}"] = {"ms_per_step": round(ms, 4), "tok_s": round(batch / ms * 1e3),
+                                       "launches_per_step": (native.launch_count() - before) // args.steps}
+            handles[-1].tokens()
+            for request in requests:
+                manager.release(request)
+        del engine, runner, manager, sampler
+        gc.collect()
+        torch.cuda.empty_cache()
+        return out
+
+    results = {}
+    for name in (() if args.only == "kernels" else args.size.split(",") if args.size else SORULIX_SIZES):
+        shape = SORULIX_SIZES[name]
+        results[name] = {"shape": dict(zip(("width", "ff", "heads", "kv_heads", "head_dim", "layer_pairs", "vocab"), shape)),
+                         "sorulix": measure(_sorulix_config(*shape), shape[-1]),
+                         "qwen3_equal_size": measure(_qwen3_like(*shape), shape[-1])}
+    kernels = _sorulix_kernels(peak, timed) if args.only in ("all", "kernels") else {}
+    return {"workload": "sorulix", "context": context, "steps": args.steps, "warmup": max(args.warmup, 3), "dtype": "bfloat16",
+            "data": "synthetic token ids, seeded random weights", "peaks": peak, "models": results, "kernels": kernels}
+
+
+def _sorulix_kernels(peak, timed) -> dict:
+    """Each new kernel alone at the 4k shape (32 heads of 128, 8 KV heads), back to back, inputs larger than L2 where
+    the kernel is bound by memory; beside it the kernel of the plain attention path at the same shape."""
+
+    import torch
+    from types import SimpleNamespace
+
+    from llm_runtime_study_b200.ops import attention_bf16, attention_rules
+    from llm_runtime_study_b200.ops import functional as F
+    from llm_runtime_study_b200.ops import sequence_state as S
+
+    dev = "cuda:0"
+    heads, kv_heads, d, page = 32, 8, 128, PAGE_SIZE
+    out = {}
+    cold = timed
+
+    def timed(fn, repeat):        # the first calls build and load libraries and size workspaces
+        fn()
+        fn()
+        return cold(fn, repeat)
+
+    slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / heads) for h in range(heads)], dtype=torch.float32, device=dev)
+
+    def attention_case(lengths, q_lens):
+        pages = sum(-(-n // page) for n in lengths)
+        table = torch.full((len(lengths), max(-(-n // page) for n in lengths)), -1, dtype=torch.int32)
+        at = 0
+        for r, n in enumerate(lengths):
+            count = -(-n // page)
+            table[r, :count] = torch.arange(at, at + count, dtype=torch.int32)
+            at += count
+        keys = torch.randn(pages, kv_heads, page, d, device=dev).bfloat16()
+        values = torch.randn(pages, kv_heads, page, d, device=dev).bfloat16()
+        q = torch.randn(sum(q_lens), heads, d, device=dev).bfloat16()
+        positions = torch.cat([torch.arange(n - m, n) for n, m in zip(lengths, q_lens)]).int().to(dev)
+        entry = torch.cat([torch.full((m,), i) for i, m in enumerate(q_lens)]).int().to(dev)
+        ctx = SimpleNamespace(all_decode=max(q_lens) == 1, num_entries=len(lengths), max_kv_len=max(lengths), max_q_len=max(q_lens),
+                              q_lens=list(q_lens), kv_lens=list(lengths), kv_len=torch.tensor(lengths, dtype=torch.int32, device=dev),
+                              positions=positions, token_entry=entry, live_parts=None)
+        return q, SimpleNamespace(keys=keys, values=values), ctx, table.to(dev)
+
+    for tokens in (2048, 8192):
+        q, cache, ctx, table = attention_case([tokens], [tokens])
+        flops = 4.0 * heads * d * tokens * (tokens + 1) / 2
+        rules = timed(lambda: attention_rules.paged_attention_rules(q, cache, ctx, table, scale=d ** -0.5, softcap=50.0, slopes=slopes, sink=True), 5)
+        ctx.__dict__.pop("_tile_maps", None)
+        plain_mma = timed(lambda: attention_bf16.prefill_attention(q, cache.keys, cache.values, positions=ctx.positions, block_table=table,
+                                                                   q_lens=ctx.q_lens, scale=d ** -0.5), 5)
+        plain_tc = timed(lambda: attention_bf16.try_paged_attention(q, cache, ctx, table, scale=d ** -0.5, window=0), 5)
+        out[f"prefill_attention_{tokens}"] = {
+            "with_rules_mma_ms": round(rules, 3), "plain_mma_ms": round(plain_mma, 3), "plain_tcgen05_ms": round(plain_tc, 3),
+            "with_rules_tflops": round(flops / rules / 1e9, 1), "plain_mma_tflops": round(flops / plain_mma / 1e9, 1),
+            "plain_tcgen05_tflops": round(flops / plain_tc / 1e9, 1),
+            "of_measured_bf16_burst": {"with_rules": round(flops / rules / 1e9 / peak["bf16_tflops"], 3),
+                                       "plain_tcgen05": round(flops / plain_tc / 1e9 / peak["bf16_tflops"], 3)}}
+    for batch, length in ((8, 2048), (32, 8192)):
+        q, cache, ctx, table = attention_case([length] * batch, [1] * batch)
+        moved = 2.0 * batch * length * kv_heads * d * 2
+        rules = timed(lambda: attention_rules.paged_attention_rules(q, cache, ctx, table, scale=d ** -0.5, softcap=50.0, slopes=slopes, sink=True), 20)
+        plain_tma = timed(lambda: attention_bf16.try_paged_attention(q, cache, ctx, table, scale=d ** -0.5, window=0), 20)
+        out[f"decode_attention_b{batch}_ctx{length}"] = {
+            "with_rules_mma_us": round(rules * 1e3, 1), "plain_tma_us": round(plain_tma * 1e3, 1), "cache_mb": round(moved / 1e6, 1),
+            "of_measured_copy": {"with_rules": round(moved / rules / 1e6 / peak["hbm_gbs"], 3),
+                                 "plain_tma": round(moved / plain_tma / 1e6 / peak["hbm_gbs"], 3)}}
+    # the scans: decoding moves every request's state in and out; a prompt is a chain of dependent steps
+    for batch in (8, 64):
+        n = batch
+        q, k, v = (torch.randn(n, heads * d, device=dev) for _ in range(3))
+        gate, beta = torch.rand(n, heads * d, device=dev), torch.rand(n, heads, device=dev)
+        state = torch.zeros(batch + 1, heads, d, d, device=dev)
+        q_start = torch.arange(batch + 1, dtype=torch.int32, device=dev)
+        slots = torch.arange(batch, dtype=torch.int32, device=dev)
+        decay = torch.full((heads,), 0.97, device=dev)
+        moved = 2.0 * batch * heads * d * d * 4
+        plain_ms = timed(lambda: S.linear_scan(q, k, v, heads=heads, qk_heads=heads, dim=d, vdim=d, state=state, q_start=q_start, slots=slots, decay=decay, silu=True), 20)
+        delta_ms = timed(lambda: S.linear_scan(q, k, v, heads=heads, qk_heads=heads, dim=d, vdim=d, state=state, q_start=q_start, slots=slots, gate=gate, beta=beta), 20)
+        out[f"scan_decode_b{batch}"] = {"decay_us": round(plain_ms * 1e3, 1), "delta_us": round(delta_ms * 1e3, 1), "state_mb": round(moved / 1e6, 1),
+                                        "of_measured_copy": {"decay": round(moved / plain_ms / 1e6 / peak["hbm_gbs"], 3),
+                                                             "delta": round(moved / delta_ms / 1e6 / peak["hbm_gbs"], 3)}}
+    n = 2048
+    q, k, v = (torch.randn(n, heads * d, device=dev) for _ in range(3))
+    gate, beta = torch.rand(n, heads * d, device=dev) * 0.1 + 0.9, torch.rand(n, heads, device=dev)
+    state = torch.zeros(2, heads, d, d, device=dev)
+    q_start = torch.tensor([0, n], dtype=torch.int32, device=dev)
+    slots = torch.zeros(1, dtype=torch.int32, device=dev)
+    kn = torch.nn.functional.normalize(k.view(n, heads, d), dim=-1).reshape(n, -1)
+    delta_ms = timed(lambda: S.linear_scan(q, kn, v, heads=heads, qk_heads=heads, dim=d, vdim=d, state=state, q_start=q_start, slots=slots, gate=gate, beta=beta), 3)
+    state.zero_()
+    decay_ms = timed(lambda: S.linear_scan(q, kn, v, heads=heads, qk_heads=heads, dim=d, vdim=d, state=state, q_start=q_start, slots=slots,
+                                           decay=torch.full((heads,), 0.97, device=dev)), 3)
+    out["scan_prefill_2048"] = {"delta_ms": round(delta_ms, 3), "decay_ms": round(decay_ms, 3),
+                                "delta_us_per_token": round(delta_ms * 1e3 / n, 3), "decay_us_per_token": round(decay_ms * 1e3 / n, 3)}
+    # element-wise kernels at 2,048 rows (inputs of tens of MB; the figure is bytes moved over the copy rate)
+    rows, ff = 2048, 12288
+    gate_up = torch.randn(rows, 2 * ff, device=dev).bfloat16()
+    ms = timed(lambda: F.glu_limit(gate_up, 7.0, 1.702), 20)
+    ref = timed(lambda: F.silu_mul(gate_up), 20)
+    moved = rows * ff * 2 * 3
+    out["glu_limit_2048x12288"] = {"us": round(ms * 1e3, 1), "silu_mul_us": round(ref * 1e3, 1),
+                                   "of_measured_copy": {"glu_limit": round(moved / ms / 1e6 / peak["hbm_gbs"], 3),
+                                                        "silu_mul": round(moved / ref / 1e6 / peak["hbm_gbs"], 3)}}
+    return out
+
+
 def run_reference(args) -> dict:
     """The unmodified reference from baseline/_ref: its own Qwen3ForCausalLM, paged cache,
     CUDA-graph decode and BatchScheduler, driven through Engine.create_scheduler()."""
@@ -641,10 +852,13 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--context", type=int, default=0, help="with --only decode: cached tokens per request (default 2048)")
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (named in config)")
-    parser.add_argument("--workload", choices=("default", "staggered14b", "decode32b"), default="default",
-                        help="default: Qwen3-8B decode/prefill; the others are the larger configurations (either --impl)")
-    parser.add_argument("--only", choices=("all", "decode", "prefill"), default="all",
-                        help="run only the decode steps or only the prefill (for profiler captures of a small case)")
+    parser.add_argument("--workload", choices=("default", "staggered14b", "decode32b", "sorulix"), default="default",
+                        help="default: Qwen3-8B decode/prefill; staggered14b, decode32b: the larger configurations (either --impl); "
+                             "sorulix: the Sorulix design beside Qwen3 at equal sizes, and its kernels alone")
+    parser.add_argument("--size", default="", help="with --workload sorulix: sizes to run, with commas (2k, 4k; default both)")
+    parser.add_argument("--only", choices=("all", "decode", "prefill", "kernels", "models"), default="all",
+                        help="run only the decode steps or only the prefill (for profiler captures of a small case); "
+                             "with --workload sorulix: only the kernels alone, or only the whole models")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU: --gpus {args.gpus} is not supported by this engine (single-GPU tier)")
@@ -653,6 +867,11 @@ def main() -> int:
         result = run_staggered_14b(args)
     elif args.workload == "decode32b":
         result = run_decode_32b(args)
+    elif args.workload == "sorulix":
+        if args.impl == "reference":
+            result = _unavailable("the reference has no model of this design")
+        else:
+            result = run_sorulix(args)
     else:
         result = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(result))

@@ -35,15 +35,19 @@ constexpr int kScanThreads = 128;
 constexpr int kScanChunk = 8;     // tokens staged in shared memory at a time
 
 // One CTA owns some columns of one head's state for one request.  A column is independent of the
-// others: S[:, c] <- D S[:, c] + k u_c.  Its d rows are spread over `rl` lanes of one warp (row i
-// belongs to lane i % rl), DPT rows per lane in registers; the two dot products over rows are
-// finished by shuffles.
-template <typename T, int DPT, bool DELTA, bool GATED>
+// others: S[:, c] <- D S[:, c] + k u_c.  Its d rows are spread over RL lanes of one warp (row i
+// belongs to lane i % RL), DPT rows per lane in registers; the two dot products over rows are
+// finished by shuffles.  RL = 4 keeps 8 neighbouring columns (one 32-byte sector of a state row) in
+// a warp, which is what a launch that mostly moves states wants (many requests, one token each);
+// RL = 16 spreads a column over more lanes and a head over sixteen times as many CTAs, which is
+// what a launch with few requests and long portions wants: its time is a chain of dependent steps,
+// and the chain per token is a quarter as long.
+template <typename T, int DPT, int RL, bool DELTA, bool GATED>
 __global__ void __launch_bounds__(kScanThreads) linear_scan_kernel(const ScanParams p) {
   extern __shared__ float smem[];
   pdl_trigger();
   pdl_wait();
-  const int rl = p.rl, cols_per_warp = 32 / rl, cols = (kScanThreads / 32) * cols_per_warp;
+  constexpr int rl = RL, cols_per_warp = 32 / rl, cols = (kScanThreads / 32) * cols_per_warp;
   const int col_blocks = (p.dv + cols - 1) / cols;
   const int h = blockIdx.x / col_blocks, cb = blockIdx.x % col_blocks;
   const int entry = blockIdx.y;
@@ -147,14 +151,24 @@ int launch_scan(const ScanParams& p, int entries, cudaStream_t stream) {
   const int dpt8 = (dpt + 7) / 8 * 8;
   const size_t smem = sizeof(float) * (static_cast<size_t>(kScanChunk) * dpt8 * p.rl * (GATED ? 3 : 2) + kScanChunk * cols + kScanChunk);
   if (smem > 48 * 1024) return B200_ERR_TOO_LARGE;
-  switch (dpt8) {
-    case 8: launch(linear_scan_kernel<T, 8, DELTA, GATED>, grid, dim3(kScanThreads), smem, stream, p); break;
-    case 16: launch(linear_scan_kernel<T, 16, DELTA, GATED>, grid, dim3(kScanThreads), smem, stream, p); break;
-    case 24: launch(linear_scan_kernel<T, 24, DELTA, GATED>, grid, dim3(kScanThreads), smem, stream, p); break;
-    case 32: launch(linear_scan_kernel<T, 32, DELTA, GATED>, grid, dim3(kScanThreads), smem, stream, p); break;
-    default: return B200_ERR_TOO_LARGE;
+#define B200_SCAN_CASE(DPT_, RL_)                                                                                      \
+  if (dpt8 == DPT_ && p.rl == RL_) {                                                                                   \
+    launch(linear_scan_kernel<T, DPT_, RL_, DELTA, GATED>, grid, dim3(kScanThreads), smem, stream, p);                 \
+    return launch_status();                                                                                            \
   }
-  return launch_status();
+  B200_SCAN_CASE(8, 4) B200_SCAN_CASE(16, 4) B200_SCAN_CASE(24, 4) B200_SCAN_CASE(32, 4)
+  B200_SCAN_CASE(8, 16) B200_SCAN_CASE(16, 16)
+#undef B200_SCAN_CASE
+  return B200_ERR_TOO_LARGE;
+}
+
+// Lanes per column for a launch: 16 where the key size needs them (more than 128 rows) or where 4 would leave most
+// of the GPU idle (fewer CTAs than two per SM); 4 otherwise.
+static int scan_row_lanes(int entries, int H, int d, int dv, int tokens, int fixed_order) {
+  if (d > 128) return 16;
+  if (fixed_order) return 4;       // the order of a column's sums must not depend on the shape of the batch
+  const int ctas4 = entries * H * ((dv + 31) / 32);
+  return (ctas4 < 2 * 148 && tokens > entries) ? 16 : 4;
 }
 
 // ---------------------------------------------- preparation of a gated delta rule's inputs
@@ -276,19 +290,20 @@ __global__ void group_norm_gate_kernel(const float* __restrict__ x, int width, i
 
 }  // namespace b200
 
+// `tokens`: rows in the batch (with `entries` it tells a batch of single tokens from one that holds portions).
+// `fixed_order`: the same lanes per column whatever the batch looks like, so that a token's bits do not depend on the cut.
 // q, k: [n, Hqk * d] rows (strides ldq, ldk), v: [n, H * dv]; element type by `dtype`.  gate (float32 [n, H * d]) selects
 // per-row factors, else `decay` ([H]) is used; beta (float32 [n, H]) selects the delta rule.  state float32 [slots, H, d, dv].
 extern "C" int b200_linear_scan(const void* q, const void* k, const void* v, int ldq, int ldk, int ldv, const float* gate, int ldg,
                                 const float* decay, const float* beta, int ldb, float* state, float* out, int ldo,
-                                const int* q_start, const int* slots, int entries, int H, int Hqk, int d, int dv, int act,
-                                int dtype, cudaStream_t stream) {
+                                const int* q_start, const int* slots, int entries, int tokens, int H, int Hqk, int d, int dv,
+                                int act, int fixed_order, int dtype, cudaStream_t stream) {
   using namespace b200;
   if (entries <= 0) return 0;
   if (H <= 0 || Hqk <= 0 || H % Hqk != 0 || d <= 0 || dv <= 0 || d > 256) return B200_ERR_BAD_SIZE;
   if ((gate == nullptr) == (decay == nullptr)) return B200_ERR_BAD_SIZE;
   ScanParams p{q, k, v, ldq, ldk, ldv, gate, ldg, decay, beta, ldb, state, out, ldo, q_start, slots, H, Hqk, d, dv, act, 1};
-  while (p.rl < 32 && (d + p.rl - 1) / p.rl > 32) p.rl *= 2;
-  while (p.rl < 4 && (d + p.rl - 1) / p.rl > 8) p.rl *= 2;
+  p.rl = scan_row_lanes(entries, H, d, dv, tokens, fixed_order);
   const bool delta = beta != nullptr, gated = gate != nullptr;
   if (delta && gated) {
     B200_DISPATCH_DTYPE(dtype, T, return (launch_scan<T, true, true>(p, entries, stream)));

@@ -13,14 +13,16 @@ from .native import call, ptr, require, stream_ptr, tag
 def linear_scan(
     q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, heads: int, qk_heads: int, dim: int, vdim: int,
     state: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor, gate: torch.Tensor | None = None,
-    decay: torch.Tensor | None = None, beta: torch.Tensor | None = None, silu: bool = False,
+    decay: torch.Tensor | None = None, beta: torch.Tensor | None = None, silu: bool = False, fixed_order: bool = False,
 ) -> torch.Tensor:
     """Per request (entry ``e`` owns rows ``q_start[e] .. q_start[e+1]-1`` and the state row ``slots[e]``) and head,
     token after token: ``S <- D S + k u^T``, ``o = S^T q`` with ``D`` the head's constant ``decay`` or the row's
     ``gate`` factors (one per key channel), and ``u = v`` or, with ``beta``, ``beta (v - (D S)^T k)``.  ``q`` and
     ``k`` are ``[N, qk_heads * dim]`` column blocks (a row stride of their own is fine), ``v`` ``[N, heads * vdim]``;
     head ``h`` reads q/k head ``h // (heads / qk_heads)``.  ``silu`` applies SiLU to q, k and v as they are read.
-    ``state`` is ``[slots, heads, dim, vdim]`` float32 and is updated in place.  Returns float32 ``[N, heads * vdim]``."""
+    ``state`` is ``[slots, heads, dim, vdim]`` float32 and is updated in place.  ``fixed_order``: every sum is formed in
+    an order that does not depend on the shape of the batch (the kernel otherwise spreads a column over more lanes when few
+    requests bring long portions), so a token's bits do not depend on the cut.  Returns float32 ``[N, heads * vdim]``."""
 
     n = q.shape[0]
     for t, name, width in ((q, "q", qk_heads * dim), (k, "k", qk_heads * dim), (v, "v", heads * vdim)):
@@ -42,8 +44,8 @@ def linear_scan(
         require(beta, "beta", dtype=torch.float32, shape=(n, heads))
     out = torch.empty((n, heads * vdim), dtype=torch.float32, device=q.device)
     call("b200_linear_scan", ptr(q), ptr(k), ptr(v), q.stride(0), k.stride(0), v.stride(0), ptr(gate), heads * dim, ptr(decay),
-         ptr(beta), heads, ptr(state), ptr(out), heads * vdim, ptr(q_start), ptr(slots), entries, heads, qk_heads, dim, vdim,
-         1 if silu else 0, tag(q.dtype), stream_ptr())
+         ptr(beta), heads, ptr(state), ptr(out), heads * vdim, ptr(q_start), ptr(slots), entries, n, heads, qk_heads, dim, vdim,
+         1 if silu else 0, 1 if fixed_order else 0, tag(q.dtype), stream_ptr())
     return out
 
 

@@ -66,7 +66,7 @@ class DecayedLinearAttention(Mixer):
         out = S.linear_scan(
             proj[:, :qk], proj[:, qk : 2 * qk], proj[:, 2 * qk : 2 * qk + vw], heads=self.num_heads, qk_heads=self.num_heads,
             dim=self.head_dim, vdim=self.value_dim, state=cache.state, q_start=ctx.q_start, slots=ctx.slots, decay=self.decays,
-            silu=True,
+            silu=True, fixed_order=self.runtime.dtype == torch.float32,
         )
         gated = S.group_norm_gate(out, self.norm_weight, self.eps, proj, gate_offset=2 * qk + vw, out_dtype=self.runtime.dtype)
         return self.o_proj(gated, torch.float32)
@@ -147,6 +147,7 @@ class GatedDeltaRule(Mixer):
         out = S.linear_scan(
             q, k, v, heads=self.num_heads, qk_heads=self.num_qk_heads, dim=self.head_dim, vdim=self.value_dim,
             state=cache.states["state"], q_start=ctx.q_start, slots=ctx.slots, gate=g, beta=beta,
+            fixed_order=self.runtime.dtype == torch.float32,
         )
         gated = S.group_norm_gate(out, self.norm_weight, self.eps, proj, gate_offset=gate_offset, gate_up=self.g_up,
                                   out_dtype=self.runtime.dtype)

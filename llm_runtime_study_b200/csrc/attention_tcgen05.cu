@@ -78,8 +78,14 @@ struct TcAttnParams {
   const int* tile_entry;
   const int* tile_start;
   const int* tile_count;
+  // rules on the scores (the one-tile kernel built with RULES): S <- cap * tanh(S * scale / cap), S <- S - slope_h * (p - t),
+  // and a sink (a key of score 0 without a value)
+  float scale, softcap;        // softcap <= 0: none
+  const float* slopes;         // [nq] or null
+  int sink;
 };
 
+template <bool RULES>
 __global__ void __launch_bounds__(kTcThreads)
 prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                  const __grid_constant__ CUtensorMap map_v, TcAttnParams p) {
@@ -236,6 +242,10 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
     float m_used = -INFINITY, l = 0.f;       // m_used in units of log2, after scaling
     bool ok = true;
+    // with rules the scores are brought to their final value in units of log2 right after they are read
+    const float scale_log2 = RULES ? 1.f : p.scale_log2;
+    const float slope = (RULES && p.slopes && row_ok) ? p.slopes[head0 + g] : 0.f;
+    const float inv_cap = (RULES && p.softcap > 0.f) ? 1.f / p.softcap : 0.f;
     for (int j = 0; j < ntiles; ++j) {
       if (!mbar_wait(s_full + (j & 1), (j >> 1) & 1)) { atomicExch(&g_attn_error, 4); ok = false; break; }
       tcgen05_fence_after();
@@ -252,6 +262,16 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         }
       }
       const int t0 = j * BN;
+      if constexpr (RULES) {
+        const float far = static_cast<float>(row_hi - t0);     // distance of the tile's first key
+#pragma unroll
+        for (int i = 0; i < BN; ++i) {
+          float x = sv[i] * p.scale;
+          // tanh(y) = 1 - 2 / (e^(2y) + 1): one exponential and one reciprocal
+          if (p.softcap > 0.f) x = p.softcap * (1.f - __fdividef(2.f, __expf(2.f * x * inv_cap) + 1.f));
+          sv[i] = (x - slope * (far - static_cast<float>(i))) * 1.4426950408889634f;
+        }
+      }
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (t0 + BN - 1 <= p_first) {          // every key of the tile is visible to every row of this CTA
 #pragma unroll
@@ -264,7 +284,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         }
       }
       const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-      const float m_new = fmaxf(m_used, m_tile * p.scale_log2);   // the scale is positive
+      const float m_new = fmaxf(m_used, m_tile * scale_log2);   // the scale is positive
       const bool grow = m_new > m_used + kRescaleStep;            // also true on the first tile (m_used = -inf)
       if (j == 0) {
         m_used = m_new;
@@ -293,7 +313,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         float e[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          e[i] = exp2_fast(fmaf(sv[c * 8 + i], p.scale_log2, neg_ref));
+          e[i] = exp2_fast(fmaf(sv[c * 8 + i], scale_log2, neg_ref));
           lsum[i & 3] += e[i];
         }
         packed[c].x = pack_bf16(e[0], e[1]);
@@ -328,6 +348,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         atomicExch(&g_attn_error, 7);
       } else {
         tcgen05_fence_after();
+        if (RULES && p.sink) l += exp2f(-m_used);      // the sink's exp(0 - reference); no visible key: infinity, a row of zeros
         const float inv = l > 0.f ? 1.f / l : 0.f;
         bf16* dst = p.out + (static_cast<size_t>(tok0 + tl) * p.nq + head0 + g) * D;
         uint32_t r[32];
@@ -786,7 +807,8 @@ extern "C" int b200_attention_tcgen05_tokens_per_pair(int group) { return 2 * b2
 static int prefill_tcgen05(const void* q, const void* k_pool, const void* v_pool, void* out, const int* positions,
                            const int* block_table, int table_stride, int page_size, int num_pages, int tokens, int nq,
                            int nkv, float scale, const int* tile_entry, const int* tile_start, const int* tile_count,
-                           int num_tiles, bool pair, cudaStream_t stream) {
+                           int num_tiles, bool pair, cudaStream_t stream, bool rules = false, float softcap = 0.f,
+                           const float* slopes = nullptr, int sink = 0) {
   if (num_tiles <= 0) return 0;
   if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || table_stride <= 0 || tokens <= 0) return B200_ERR_BAD_SIZE;
   if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64) return B200_ERR_BAD_SIZE;
@@ -803,6 +825,10 @@ static int prefill_tcgen05(const void* q, const void* k_pool, const void* v_pool
   p.gs = p.group < 16 ? p.group : 16;
   p.slices = (p.group + p.gs - 1) / p.gs;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.scale = scale;
+  p.softcap = softcap;
+  p.slopes = slopes;
+  p.sink = sink;
   p.tile_entry = tile_entry;
   p.tile_start = tile_start;
   p.tile_count = tile_count;
@@ -831,13 +857,29 @@ static int prefill_tcgen05(const void* q, const void* k_pool, const void* v_pool
     static DeviceOnce once;
     if (int e = configure_once(once, prefill_attention_pair_kernel, smem)) return e;
     launch(prefill_attention_pair_kernel, grid, dim3(kPairThreads), smem, stream, map_q, map_k, map_v, p);
+  } else if (rules) {
+    constexpr size_t smem = SMEM_TILES + kBarrierBytes;
+    static DeviceOnce once;
+    if (int e = configure_once(once, prefill_attention_tcgen05_kernel<true>, smem)) return e;
+    launch(prefill_attention_tcgen05_kernel<true>, grid, dim3(kTcThreads), smem, stream, map_q, map_k, map_v, p);
   } else {
     constexpr size_t smem = SMEM_TILES + kBarrierBytes;
     static DeviceOnce once;
-    if (int e = configure_once(once, prefill_attention_tcgen05_kernel, smem)) return e;
-    launch(prefill_attention_tcgen05_kernel, grid, dim3(kTcThreads), smem, stream, map_q, map_k, map_v, p);
+    if (int e = configure_once(once, prefill_attention_tcgen05_kernel<false>, smem)) return e;
+    launch(prefill_attention_tcgen05_kernel<false>, grid, dim3(kTcThreads), smem, stream, map_q, map_k, map_v, p);
   }
   return launch_status();
+}
+
+// The one-tile kernel with rules on the scores: softcap (<= 0: none), slopes ([nq] floats or null), sink (0 or 1).
+extern "C" int b200_attention_prefill_tcgen05_rules(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                                    const int* positions, const int* block_table, int table_stride,
+                                                    int page_size, int num_pages, int tokens, int nq, int nkv, float scale,
+                                                    float softcap, const float* slopes, int sink,
+                                                    const int* tile_entry, const int* tile_start, const int* tile_count,
+                                                    int num_tiles, cudaStream_t stream) {
+  return prefill_tcgen05(q, k_pool, v_pool, out, positions, block_table, table_stride, page_size, num_pages, tokens, nq, nkv,
+                         scale, tile_entry, tile_start, tile_count, num_tiles, false, stream, true, softcap, slopes, sink);
 }
 
 extern "C" int b200_attention_prefill_tcgen05(const void* q, const void* k_pool, const void* v_pool, void* out,

@@ -328,13 +328,14 @@ extern "C" int b200_delta_prepare(const void* proj, int ld, int b_off, int a_off
   DeltaPrepareParams p{proj, ld, b_off, a_off, rank, taps, ntaps, conv_state, a_log, dt_bias, a_up, q, k, v, g, beta,
                        q_start, slots, token_entry, H, G, d, dv, unit_eps, q_scale};
   const size_t smem = sizeof(float) * (static_cast<size_t>(2) * G * d + static_cast<size_t>(H) * dv + rank);
+  // the opt-in to large shared memory is made once per device, for the largest row this kernel takes
   static DeviceOnce once_f32, once_bf16;
   if (smem > 200 * 1024) return B200_ERR_TOO_LARGE;
   if (dtype == kF32) {
-    if (int e = configure_once(once_f32, delta_prepare_kernel<float>, smem > 48 * 1024 ? 200 * 1024 : 0)) return e;
+    if (int e = configure_once(once_f32, delta_prepare_kernel<float>, 200 * 1024)) return e;
     launch(delta_prepare_kernel<float>, dim3(n), dim3(256), smem, stream, p);
   } else if (dtype == kBF16) {
-    if (int e = configure_once(once_bf16, delta_prepare_kernel<__nv_bfloat16>, smem > 48 * 1024 ? 200 * 1024 : 0)) return e;
+    if (int e = configure_once(once_bf16, delta_prepare_kernel<__nv_bfloat16>, 200 * 1024)) return e;
     launch(delta_prepare_kernel<__nv_bfloat16>, dim3(n), dim3(256), smem, stream, p);
   } else {
     return B200_ERR_BAD_DTYPE;

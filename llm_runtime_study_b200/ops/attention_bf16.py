@@ -59,6 +59,8 @@ _TC_TABLE = {
     "b200_attention_tcgen05_tokens_per_tile": [c_int],
     "b200_attention_prefill_tcgen05": [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_int, c_int, c_float] + [c_void_p] * 3 + [c_int, c_void_p],
     "b200_attention_prefill_tcgen05_pair": [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_int, c_int, c_float] + [c_void_p] * 3 + [c_int, c_void_p],
+    "b200_attention_prefill_tcgen05_rules": [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_int]
+                                            + [c_void_p] * 3 + [c_int, c_void_p],
 }
 # Two row tiles per CTA (one CTA per SM, 128 keys a tile) for steps with a portion of at least this many tokens
 # (measured at the Qwen3-8B geometry: half again as fast at 2,048 new tokens and beyond, 7 % slower at 1,024);

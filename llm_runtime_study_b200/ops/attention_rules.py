@@ -10,8 +10,9 @@ import torch
 from . import attention_bf16, native
 from . import functional as F
 
-# "mma": the tensor-core kernels wherever they take the shape; "simt": the CUDA-core kernel everywhere
-BACKEND = os.environ.get("LLM_RUNTIME_STUDY_B200_ATTENTION_RULES", "mma")
+# "tcgen05": the tensor-core kernels wherever they take the shape (tcgen05 for prompt portions of head size 64 and
+# 128, mma.sync otherwise); "mma": mma.sync only; "simt": the CUDA-core kernel everywhere
+BACKEND = os.environ.get("LLM_RUNTIME_STUDY_B200_ATTENTION_RULES", "tcgen05")
 
 
 def tensor_core_supported(q: torch.Tensor, cache: Any) -> bool:
@@ -28,11 +29,12 @@ def paged_attention_rules(q: torch.Tensor, cache: Any, ctx: Any, table: torch.Te
 
     float32 runtime, and shapes no tensor-core kernel takes (values of another head size than the keys): the
     CUDA-core kernel (one warp per token and head, float32 arithmetic, tiles of 32 keys from key 0, so the order
-    of every sum depends on the token's position alone).  bfloat16 runtime: the mma.sync kernels of the plain
-    attention, built a second time with the rules applied to the score tile (one for batches that hold prompt
-    portions, a split-sequence one with a merge for batches of single decoded tokens)."""
+    of every sum depends on the token's position alone).  bfloat16 runtime: the kernels of the plain attention,
+    built a second time with the rules applied to the score tile: for batches that hold prompt portions the tcgen05
+    kernel with one row tile per CTA (head sizes 64 and 128, portions of 32 tokens and more, no window) or the
+    mma.sync kernel; for batches of single decoded tokens the split-sequence mma.sync kernel with its merge."""
 
-    if BACKEND == "mma" and tensor_core_supported(q, cache):
+    if BACKEND in ("mma", "tcgen05") and tensor_core_supported(q, cache):
         n, nq, d = q.shape
         keys, values = cache.keys, cache.values
         _, _, _, nkv, page_size, gs, slices = attention_bf16._geometry(q, keys)
@@ -49,6 +51,19 @@ def paged_attention_rules(q: torch.Tensor, cache: Any, ctx: Any, table: torch.Te
                 library=lib, launches=2 if splits > 1 else 1)
             return out
         maps = ctx.__dict__.setdefault("_tile_maps", {})
+        if (BACKEND == "tcgen05" and attention_bf16.PREFILL_BACKEND == "tcgen05" and attention_bf16.tc_supported(d, page_size, window)
+                and ctx.max_q_len >= attention_bf16.TC_MIN_PORTION):
+            per_tile = 128 // gs
+            key = ("tc", per_tile)
+            if key not in maps:
+                maps[key] = attention_bf16.tile_map(ctx.q_lens, per_tile, q.device, ctx.kv_lens)
+            tiles, count = maps[key]
+            native.call(
+                "b200_attention_prefill_tcgen05_rules", q.data_ptr(), keys.data_ptr(), values.data_ptr(), out.data_ptr(),
+                ctx.positions.data_ptr(), table.data_ptr(), table.shape[1], page_size, keys.shape[0], n, nq, nkv, float(scale),
+                float(softcap), native.ptr(slopes), 1 if sink else 0, tiles[0].data_ptr(), tiles[1].data_ptr(), tiles[2].data_ptr(),
+                count, native.stream_ptr(), library=attention_bf16.tc_library_name(d))
+            return out
         per_tile = 64 // gs
         if per_tile not in maps:
             maps[per_tile] = attention_bf16.tile_map(ctx.q_lens, per_tile, q.device, ctx.kv_lens)

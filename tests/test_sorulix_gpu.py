@@ -140,8 +140,9 @@ def test_a_far_key_among_hundreds_and_the_sink_on_the_first_tokens():
     (5, 1, 128, 4.0, True, True, 32),
 ])
 def test_tensor_core_attention_rules_against_the_cuda_core_kernel(nq, nkv, d, softcap, slopes, sink, page):
-    """The mma.sync kernels with rules (prompt portions beside single tokens; single tokens of long sequences cut
-    into parts and merged) against the float32 CUDA-core kernel on the same pages."""
+    """The tensor-core kernels with rules (prompt portions beside single tokens: tcgen05 for head sizes 64 and 128,
+    mma.sync for the others; long portions behind a cached prefix; single tokens of long sequences cut into parts and
+    merged) against the float32 CUDA-core kernel on the same pages."""
 
     from types import SimpleNamespace
 
@@ -150,7 +151,7 @@ def test_tensor_core_attention_rules_against_the_cuda_core_kernel(nq, nkv, d, so
 
     torch.manual_seed(nq * d)
     slope = plain.distance_slopes(nq).float().to(DEV) if slopes else None
-    for lengths, q_lens in (([70, 200, 33, 1], [70, 3, 1, 1]), ([2500, 700, 64], [1, 1, 1])):
+    for lengths, q_lens in (([70, 200, 33, 1], [70, 3, 1, 1]), ([900, 130], [500, 130]), ([2500, 700, 64], [1, 1, 1])):
         table, pages = _pages(sum(lengths), page, lengths)
         table = table.to(DEV)
         keys = torch.randn(pages, nkv, page, d, device=DEV).bfloat16()
@@ -159,7 +160,7 @@ def test_tensor_core_attention_rules_against_the_cuda_core_kernel(nq, nkv, d, so
         q = (2 * torch.randn(n, nq, d, device=DEV)).bfloat16()
         positions = torch.cat([torch.arange(L - m, L) for L, m in zip(lengths, q_lens)]).int().to(DEV)
         entry = torch.cat([torch.full((m,), i) for i, m in enumerate(q_lens)]).int().to(DEV)
-        ctx = SimpleNamespace(all_decode=max(q_lens) == 1, num_entries=len(lengths), max_kv_len=max(lengths), q_lens=q_lens,
+        ctx = SimpleNamespace(all_decode=max(q_lens) == 1, num_entries=len(lengths), max_kv_len=max(lengths), max_q_len=max(q_lens), q_lens=q_lens,
                               kv_lens=lengths, kv_len=torch.tensor(lengths, dtype=torch.int32, device=DEV), positions=positions,
                               token_entry=entry)
         cache = SimpleNamespace(keys=keys, values=values)

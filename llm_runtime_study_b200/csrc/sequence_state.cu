@@ -29,10 +29,11 @@ struct ScanParams {
   float* out; int ldo;                            // [n, H * dv]
   const int* q_start; const int* slots;           // per entry: first token, request slot
   int H, Hqk, d, dv, act, rl;                     // act 1: silu on q, k, v as they are read; rl: lanes that share a column
+  int chunk;                                      // tokens staged in shared memory at a time
 };
 
 constexpr int kScanThreads = 128;
-constexpr int kScanChunk = 8;     // tokens staged in shared memory at a time
+constexpr int kScanChunk = 16;    // tokens staged in shared memory at a time, where they fit (else half as many)
 
 // One CTA owns some columns of one head's state for one request.  A column is independent of the
 // others: S[:, c] <- D S[:, c] + k u_c.  Its d rows are spread over RL lanes of one warp (row i
@@ -69,17 +70,17 @@ __global__ void __launch_bounds__(kScanThreads) linear_scan_kernel(const ScanPar
     S[ii] = (live && i < d) ? sbase[static_cast<size_t>(i) * dv + col] : 0.f;
   }
   float* ks = smem;                              // [chunk][dp]
-  float* qs = ks + kScanChunk * dp;              // [chunk][dp]
-  float* gs = qs + kScanChunk * dp;              // [chunk][dp] (gated only)
-  float* vs = gs + (GATED ? kScanChunk * dp : 0); // [chunk][cols]
-  float* bs = vs + kScanChunk * cols;            // [chunk]
+  float* qs = ks + p.chunk * dp;              // [chunk][dp]
+  float* gs = qs + p.chunk * dp;              // [chunk][dp] (gated only)
+  float* vs = gs + (GATED ? p.chunk * dp : 0); // [chunk][cols]
+  float* bs = vs + p.chunk * cols;            // [chunk]
   const float dec = GATED ? 1.f : p.decay[h];
   const T* qg = static_cast<const T*>(p.q);
   const T* kg = static_cast<const T*>(p.k);
   const T* vg = static_cast<const T*>(p.v);
 
-  for (int t0 = t_begin; t0 < t_end; t0 += kScanChunk) {
-    const int count = min(kScanChunk, t_end - t0);
+  for (int t0 = t_begin; t0 < t_end; t0 += p.chunk) {
+    const int count = min(p.chunk, t_end - t0);
     __syncthreads();
     for (int idx = threadIdx.x; idx < count * dp; idx += kScanThreads) {
       const int tt = idx / dp, i = idx % dp;
@@ -143,13 +144,15 @@ __global__ void __launch_bounds__(kScanThreads) linear_scan_kernel(const ScanPar
 }
 
 template <typename T, bool DELTA, bool GATED>
-int launch_scan(const ScanParams& p, int entries, cudaStream_t stream) {
+int launch_scan(ScanParams p, int entries, cudaStream_t stream) {
   const int dpt = (p.d + p.rl - 1) / p.rl;
   const int cols = (kScanThreads / 32) * (32 / p.rl);
   dim3 grid(p.H * ((p.dv + cols - 1) / cols), entries);
   if (grid.y > 65535) return B200_ERR_TOO_LARGE;
   const int dpt8 = (dpt + 7) / 8 * 8;
-  const size_t smem = sizeof(float) * (static_cast<size_t>(kScanChunk) * dpt8 * p.rl * (GATED ? 3 : 2) + kScanChunk * cols + kScanChunk);
+  const auto bytes = [&](int chunk) { return sizeof(float) * (static_cast<size_t>(chunk) * dpt8 * p.rl * (GATED ? 3 : 2) + chunk * cols + chunk); };
+  p.chunk = bytes(kScanChunk) <= 48 * 1024 ? kScanChunk : kScanChunk / 2;
+  const size_t smem = bytes(p.chunk);
   if (smem > 48 * 1024) return B200_ERR_TOO_LARGE;
 #define B200_SCAN_CASE(DPT_, RL_)                                                                                      \
   if (dpt8 == DPT_ && p.rl == RL_) {                                                                                   \
@@ -157,6 +160,7 @@ int launch_scan(const ScanParams& p, int entries, cudaStream_t stream) {
     return launch_status();                                                                                            \
   }
   B200_SCAN_CASE(8, 4) B200_SCAN_CASE(16, 4) B200_SCAN_CASE(24, 4) B200_SCAN_CASE(32, 4)
+  B200_SCAN_CASE(8, 8) B200_SCAN_CASE(16, 8) B200_SCAN_CASE(24, 8) B200_SCAN_CASE(32, 8)
   B200_SCAN_CASE(8, 16) B200_SCAN_CASE(16, 16)
 #undef B200_SCAN_CASE
   return B200_ERR_TOO_LARGE;
@@ -167,8 +171,13 @@ int launch_scan(const ScanParams& p, int entries, cudaStream_t stream) {
 static int scan_row_lanes(int entries, int H, int d, int dv, int tokens, int fixed_order) {
   if (d > 128) return 16;
   if (fixed_order) return 4;       // the order of a column's sums must not depend on the shape of the batch
+  static int wide = -1;            // LLM_RUNTIME_STUDY_B200_SCAN_LANES: 8 or 16 lanes for launches with few long portions
+  if (wide < 0) {
+    const char* e = getenv("LLM_RUNTIME_STUDY_B200_SCAN_LANES");
+    wide = (e && atoi(e) == 8) ? 8 : 16;
+  }
   const int ctas4 = entries * H * ((dv + 31) / 32);
-  return (ctas4 < 2 * 148 && tokens > entries) ? 16 : 4;
+  return (ctas4 < 2 * 148 && tokens > entries) ? wide : 4;
 }
 
 // ---------------------------------------------- preparation of a gated delta rule's inputs

@@ -695,7 +695,7 @@ def _sorulix_kernels(peak, timed) -> dict:
                                                                    q_lens=ctx.q_lens, scale=d ** -0.5), 5)
         plain_tc = timed(lambda: attention_bf16.try_paged_attention(q, cache, ctx, table, scale=d ** -0.5, window=0), 5)
         out[f"prefill_attention_{tokens}"] = {
-            "with_rules_mma_ms": round(rules, 3), "plain_mma_ms": round(plain_mma, 3), "plain_tcgen05_ms": round(plain_tc, 3),
+            "with_rules_ms": round(rules, 3), "plain_mma_ms": round(plain_mma, 3), "plain_tcgen05_ms": round(plain_tc, 3),
             "with_rules_tflops": round(flops / rules / 1e9, 1), "plain_mma_tflops": round(flops / plain_mma / 1e9, 1),
             "plain_tcgen05_tflops": round(flops / plain_tc / 1e9, 1),
             "of_measured_bf16_burst": {"with_rules": round(flops / rules / 1e9 / peak["bf16_tflops"], 3),
@@ -706,7 +706,7 @@ def _sorulix_kernels(peak, timed) -> dict:
         rules = timed(lambda: attention_rules.paged_attention_rules(q, cache, ctx, table, scale=d ** -0.5, softcap=50.0, slopes=slopes, sink=True), 20)
         plain_tma = timed(lambda: attention_bf16.try_paged_attention(q, cache, ctx, table, scale=d ** -0.5, window=0), 20)
         out[f"decode_attention_b{batch}_ctx{length}"] = {
-            "with_rules_mma_us": round(rules * 1e3, 1), "plain_tma_us": round(plain_tma * 1e3, 1), "cache_mb": round(moved / 1e6, 1),
+            "with_rules_us": round(rules * 1e3, 1), "plain_tma_us": round(plain_tma * 1e3, 1), "cache_mb": round(moved / 1e6, 1),
             "of_measured_copy": {"with_rules": round(moved / rules / 1e6 / peak["hbm_gbs"], 3),
                                  "plain_tma": round(moved / plain_tma / 1e6 / peak["hbm_gbs"], 3)}}
     # the scans: decoding moves every request's state in and out; a prompt is a chain of dependent steps

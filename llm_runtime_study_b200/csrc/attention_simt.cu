@@ -61,11 +61,15 @@ paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_poo
     if (valid) {
       const T* krow = k_pool + ((static_cast<size_t>(page) * nkv + kvh) * page_size + t % page_size) * d;
       float dot = 0.f;
-      for (int i = 0; i < d; i += VN) {
-        float f[VN];
-        Vec<T>::unpack(*reinterpret_cast<const typename Vec<T>::type*>(krow + i), f);
+      if (d % VN == 0) {         // rows of keys then start on 16-byte boundaries
+        for (int i = 0; i < d; i += VN) {
+          float f[VN];
+          Vec<T>::unpack(*reinterpret_cast<const typename Vec<T>::type*>(krow + i), f);
 #pragma unroll
-        for (int e = 0; e < VN; ++e) dot = fmaf(qs[i + e], f[e], dot);
+          for (int e = 0; e < VN; ++e) dot = fmaf(qs[i + e], f[e], dot);
+        }
+      } else {
+        for (int i = 0; i < d; ++i) dot = fmaf(qs[i], to_float(krow[i]), dot);
       }
       s = dot * scale;
       if (softcap > 0.f) s = softcap * tanhf(s * inv_cap);
@@ -114,7 +118,7 @@ extern "C" int b200_paged_attention_simt_rules(
     int dtype, cudaStream_t stream) {
   using namespace b200;
   if (n <= 0) return 0;
-  if (d <= 0 || d % 8 != 0 || dv <= 0 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0)
+  if (d <= 0 || dv <= 0 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0)
     return B200_ERR_BAD_SIZE;
   if (d > 32 * kMaxChunks || dv > 32 * kMaxChunks) return B200_ERR_TOO_LARGE;
   dim3 grid(n, (nq + 3) / 4);

@@ -226,8 +226,6 @@ def paged_attention_simt_rules(
     dv = v_pool.shape[3]
     if dk != d or tuple(v_pool.shape[:3]) != tuple(k_pool.shape[:3]):
         raise KernelError(f"q head size {d}, key pool {tuple(k_pool.shape)} and value pool {tuple(v_pool.shape)} do not fit")
-    if d % 8:
-        raise KernelError(f"head size {d} is not a multiple of 8")
     require(positions, "positions", dtype=torch.int32, shape=(n,))
     require(token_entry, "token_entry", dtype=torch.int32, shape=(n,))
     require(block_table, "block_table", dtype=torch.int32, dims=2)

@@ -175,8 +175,8 @@ class SinkAttention(Mixer):
             raise ValueError("attention sizes must be positive")
         if num_heads % num_kv_heads:
             raise ValueError(f"num_heads {num_heads} is not a multiple of num_kv_heads {num_kv_heads}")
-        if head_dim % 8 or head_dim > 256 or value_dim > 256:
-            raise ValueError(f"head_dim {head_dim} must be a multiple of 8, and both head sizes at most 256: no kernel takes others")
+        if head_dim > 256 or value_dim > 256:
+            raise ValueError(f"head sizes {head_dim} and {value_dim} must be at most 256: no kernel takes larger ones")
         if temperature is not None and int(temperature[1]) <= 0:
             raise ValueError("the temperature's period must be positive")
         if softcap is not None and softcap <= 0:

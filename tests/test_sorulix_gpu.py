@@ -47,7 +47,7 @@ def _pages(n_tokens, page, lengths):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nq,nkv,d,dv,softcap,slopes,sink,page", [
     (4, 2, 16, 24, 1.5, True, True, 4), (3, 3, 8, 8, 0.0, False, True, 16), (2, 1, 96, 32, 30.0, True, False, 8),
-    (8, 1, 32, 40, 0.0, True, True, 16),
+    (8, 1, 32, 40, 0.0, True, True, 16), (2, 1, 12, 20, 3.0, True, True, 4),
 ])
 def test_attention_rules_against_plain(dtype, nq, nkv, d, dv, softcap, slopes, sink, page):
     """Row norm, temperature and page write, then attention with cap, distance bias and sink, for two

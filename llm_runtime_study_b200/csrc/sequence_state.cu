@@ -29,11 +29,11 @@ struct ScanParams {
   float* out; int ldo;                            // [n, H * dv]
   const int* q_start; const int* slots;           // per entry: first token, request slot
   int H, Hqk, d, dv, act, rl;                     // act 1: silu on q, k, v as they are read; rl: lanes that share a column
-  int chunk;                                      // tokens staged in shared memory at a time
 };
 
 constexpr int kScanThreads = 128;
-constexpr int kScanChunk = 16;    // tokens staged in shared memory at a time, where they fit (else half as many)
+// tokens staged in shared memory at a time: 16, or 8 where a token's rows are more than 128 wide
+constexpr int scan_chunk(int dpt, int rl) { return dpt * rl <= 128 ? 16 : 8; }
 
 // One CTA owns some columns of one head's state for one request.  A column is independent of the
 // others: S[:, c] <- D S[:, c] + k u_c.  Its d rows are spread over RL lanes of one warp (row i
@@ -49,6 +49,10 @@ __global__ void __launch_bounds__(kScanThreads) linear_scan_kernel(const ScanPar
   pdl_trigger();
   pdl_wait();
   constexpr int rl = RL, cols_per_warp = 32 / rl, cols = (kScanThreads / 32) * cols_per_warp;
+  constexpr int dp = DPT * rl;                          // rows padded to dp >= d; the padding holds zeros
+  constexpr int CHUNK = scan_chunk(DPT, RL);            // tokens staged in shared memory at a time
+  constexpr int EPT = CHUNK * dp / kScanThreads;        // staged elements of k (q, g) per thread
+  constexpr int VPT = (CHUNK * cols + kScanThreads - 1) / kScanThreads;
   const int col_blocks = (p.dv + cols - 1) / cols;
   const int h = blockIdx.x / col_blocks, cb = blockIdx.x % col_blocks;
   const int entry = blockIdx.y;
@@ -57,56 +61,80 @@ __global__ void __launch_bounds__(kScanThreads) linear_scan_kernel(const ScanPar
   const int col_local = warp * cols_per_warp + lane % cols_per_warp;
   const int col = cb * cols + col_local;
   const bool live = col < p.dv;
-  const int d = p.d, dv = p.dv, dp = DPT * rl;          // rows padded to dp >= d; the padding holds zeros
+  const int d = p.d, dv = p.dv;
   const int hqk = h / (p.H / p.Hqk);
   const int t_begin = p.q_start[entry], t_end = p.q_start[entry + 1];
   const int slot = p.slots[entry];
   float* sbase = p.state + (static_cast<size_t>(slot) * p.H + h) * d * dv;
 
+  float* ks = smem;                              // [chunk][dp]
+  float* qs = ks + CHUNK * dp;                   // [chunk][dp]
+  float* gs = qs + CHUNK * dp;                   // [chunk][dp] (gated only)
+  float* vs = gs + (GATED ? CHUNK * dp : 0);     // [chunk][cols]
+  float* bs = vs + CHUNK * cols;                 // [chunk]
+  const float dec = GATED ? 1.f : p.decay[h];
+  const T* qg = static_cast<const T*>(p.q);
+  const T* kg = static_cast<const T*>(p.k);
+  const T* vg = static_cast<const T*>(p.v);
+
+  // The rows of the next chunk are asked for before the tokens of this one are worked through, and land in
+  // registers; they go to shared memory (SiLU applied once per element) when this chunk is done.
+  float rk[EPT], rq[EPT], rg[EPT], rv[VPT], rb = 0.f;
+  auto fetch = [&](int t0, int count) {
+#pragma unroll
+    for (int e = 0; e < EPT; ++e) {
+      if (e * kScanThreads >= count * dp) break;       // a single decoded token fills one round, not sixteen
+      const int idx = threadIdx.x + e * kScanThreads;
+      const int tt = idx / dp, i = idx % dp;
+      rk[e] = rq[e] = rg[e] = 0.f;
+      if (tt < count && i < d) {
+        const size_t row = static_cast<size_t>(t0 + tt);
+        rk[e] = to_float(kg[row * p.ldk + hqk * d + i]);
+        rq[e] = to_float(qg[row * p.ldq + hqk * d + i]);
+        if (GATED) rg[e] = p.gate[row * p.ldg + h * d + i];
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < VPT; ++e) {
+      if (e * kScanThreads >= count * cols) break;
+      const int idx = threadIdx.x + e * kScanThreads;
+      const int tt = idx / cols, c = cb * cols + idx % cols;
+      rv[e] = (tt < count && c < dv) ? to_float(vg[static_cast<size_t>(t0 + tt) * p.ldv + h * dv + c]) : 0.f;
+    }
+    if (DELTA && threadIdx.x < count) rb = p.beta[static_cast<size_t>(t0 + threadIdx.x) * p.ldb + h];
+  };
+  auto stash = [&](int count) {
+#pragma unroll
+    for (int e = 0; e < EPT; ++e) {
+      if (e * kScanThreads >= count * dp) break;
+      const int idx = threadIdx.x + e * kScanThreads;
+      ks[idx] = p.act ? silu_f(rk[e]) : rk[e];
+      qs[idx] = p.act ? silu_f(rq[e]) : rq[e];
+      if (GATED) gs[idx] = rg[e];
+    }
+#pragma unroll
+    for (int e = 0; e < VPT; ++e) {
+      if (e * kScanThreads >= count * cols) break;
+      const int idx = threadIdx.x + e * kScanThreads;
+      if (idx < CHUNK * cols) vs[idx] = p.act ? silu_f(rv[e]) : rv[e];
+    }
+    if (DELTA && threadIdx.x < CHUNK) bs[threadIdx.x] = rb;
+  };
+
+  fetch(t_begin, min(CHUNK, t_end - t_begin));
   float S[DPT];
 #pragma unroll
   for (int ii = 0; ii < DPT; ++ii) {
     const int i = ii * rl + r;
     S[ii] = (live && i < d) ? sbase[static_cast<size_t>(i) * dv + col] : 0.f;
   }
-  float* ks = smem;                              // [chunk][dp]
-  float* qs = ks + p.chunk * dp;              // [chunk][dp]
-  float* gs = qs + p.chunk * dp;              // [chunk][dp] (gated only)
-  float* vs = gs + (GATED ? p.chunk * dp : 0); // [chunk][cols]
-  float* bs = vs + p.chunk * cols;            // [chunk]
-  const float dec = GATED ? 1.f : p.decay[h];
-  const T* qg = static_cast<const T*>(p.q);
-  const T* kg = static_cast<const T*>(p.k);
-  const T* vg = static_cast<const T*>(p.v);
 
-  for (int t0 = t_begin; t0 < t_end; t0 += p.chunk) {
-    const int count = min(p.chunk, t_end - t0);
+  for (int t0 = t_begin; t0 < t_end; t0 += CHUNK) {
+    const int count = min(CHUNK, t_end - t0);
+    __syncthreads();            // every warp is through the chunk before
+    stash(count);
     __syncthreads();
-    for (int idx = threadIdx.x; idx < count * dp; idx += kScanThreads) {
-      const int tt = idx / dp, i = idx % dp;
-      const size_t row = static_cast<size_t>(t0 + tt);
-      float kv = 0.f, qv = 0.f, gv = 0.f;
-      if (i < d) {
-        kv = to_float(kg[row * p.ldk + hqk * d + i]);
-        qv = to_float(qg[row * p.ldq + hqk * d + i]);
-        if (p.act) { kv = silu_f(kv); qv = silu_f(qv); }
-        if (GATED) gv = p.gate[row * p.ldg + h * d + i];
-      }
-      ks[idx] = kv;
-      qs[idx] = qv;
-      if (GATED) gs[idx] = gv;
-    }
-    for (int idx = threadIdx.x; idx < count * cols; idx += kScanThreads) {
-      const int tt = idx / cols, c = cb * cols + idx % cols;
-      float vv = 0.f;
-      if (c < dv) {
-        vv = to_float(vg[static_cast<size_t>(t0 + tt) * p.ldv + h * dv + c]);
-        if (p.act) vv = silu_f(vv);
-      }
-      vs[idx] = vv;
-    }
-    if (DELTA && threadIdx.x < count) bs[threadIdx.x] = p.beta[static_cast<size_t>(t0 + threadIdx.x) * p.ldb + h];
-    __syncthreads();
+    if (t0 + CHUNK < t_end) fetch(t0 + CHUNK, min(CHUNK, t_end - t0 - CHUNK));
     for (int tt = 0; tt < count; ++tt) {
       const float* kt = ks + tt * dp;
       const float* qt = qs + tt * dp;
@@ -121,6 +149,7 @@ __global__ void __launch_bounds__(kScanThreads) linear_scan_kernel(const ScanPar
       float u = vs[tt * cols + col_local];
       if (DELTA) {
         float sum = (dot[0] + dot[1]) + (dot[2] + dot[3]);
+#pragma unroll
         for (int o = cols_per_warp; o < 32; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
         u = bs[tt] * (u - sum);
       }
@@ -132,6 +161,7 @@ __global__ void __launch_bounds__(kScanThreads) linear_scan_kernel(const ScanPar
         acc[ii & 3] = fmaf(S[ii], qt[i], acc[ii & 3]);
       }
       float o_sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+#pragma unroll
       for (int o = cols_per_warp; o < 32; o <<= 1) o_sum += __shfl_xor_sync(0xffffffffu, o_sum, o);
       if (live && r == 0) p.out[static_cast<size_t>(t0 + tt) * p.ldo + h * dv + col] = o_sum;
     }
@@ -150,9 +180,8 @@ int launch_scan(ScanParams p, int entries, cudaStream_t stream) {
   dim3 grid(p.H * ((p.dv + cols - 1) / cols), entries);
   if (grid.y > 65535) return B200_ERR_TOO_LARGE;
   const int dpt8 = (dpt + 7) / 8 * 8;
-  const auto bytes = [&](int chunk) { return sizeof(float) * (static_cast<size_t>(chunk) * dpt8 * p.rl * (GATED ? 3 : 2) + chunk * cols + chunk); };
-  p.chunk = bytes(kScanChunk) <= 48 * 1024 ? kScanChunk : kScanChunk / 2;
-  const size_t smem = bytes(p.chunk);
+  const int chunk = scan_chunk(dpt8, p.rl);
+  const size_t smem = sizeof(float) * (static_cast<size_t>(chunk) * dpt8 * p.rl * (GATED ? 3 : 2) + chunk * cols + chunk);
   if (smem > 48 * 1024) return B200_ERR_TOO_LARGE;
 #define B200_SCAN_CASE(DPT_, RL_)                                                                                      \
   if (dpt8 == DPT_ && p.rl == RL_) {                                                                                   \

@@ -469,3 +469,86 @@ def test_greedy_generation_through_the_engine(setup):
         if event.token_id is not None:
             got[index].append(event.token_id)
     assert got == want
+
+
+def test_command_line_and_trace_runner(tmp_path):
+    """The command line writes a folder of random weights for the design and generates from it; the trace runner,
+    started as a program with four request slots, replays a mixed trace on that folder."""
+
+    import io
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    from llm_runtime_study_b200.cli import main
+    from llm_runtime_study_b200.weights import Checkpoint
+
+    config = helpers.SORULIX_B
+    config_path = tmp_path / "config.json"
+    config_path.write_text(json.dumps(config))
+    out, err = io.StringIO(), io.StringIO()
+    code = main(["--model", str(tmp_path / "m"), "--random-weights", str(config_path), "--weights-seed", "4",
+                 "--prompt-ids", "5 17 3 90", "--max-new-tokens", "5", "--max-seq-len", "64", "--dtype", "float32", "--no-stream"],
+                output=out, error=err)
+    assert code == 0, err.getvalue()
+    generated = [int(t) for t in out.getvalue().splitlines()[0].split()]
+    weights = Checkpoint.from_model_dir(tmp_path / "m").get_tensors()
+    tokens = [5, 17, 3, 90]
+    for got in generated:
+        logits = plain.forward(weights, config, tokens)[-1]
+        top = torch.topk(logits, 2).values
+        if float(top[0] - top[1]) < 1e-4:        # a tie: either token is right, and what follows differs
+            break
+        assert got == int(logits.argmax())
+        tokens.append(got)
+    rng = random.Random(2)
+    requests = {f"q{i}": helpers.random_tokens(rng, config["vocab"], n) for i, n in enumerate([9, 30, 2, 17, 40])}
+    steps = helpers.trace_mixed(requests, rng, live_max=4, tail=5)
+    root = Path(__file__).resolve().parent.parent
+    run = subprocess.run([sys.executable, str(root / "bin" / "trace_run"), "--model", str(tmp_path / "m"), "--dtype", "float32",
+                          "--out", str(tmp_path / "out"), "--max-tokens", str(helpers.pool_tokens(steps))],
+                         input=helpers.dump_trace(steps), capture_output=True, text=True, timeout=600)
+    assert run.returncode == 0, run.stderr[-2000:]
+    assert [line for line in run.stdout.splitlines() if line.startswith("done ")] == [f"done {s['step']}" for s in steps]
+    outputs = {s["step"]: torch.from_numpy(np.fromfile(tmp_path / "out" / f"{s['step']}.f32", dtype="<f4").reshape(-1, config["vocab"]))
+               for s in steps if any(e["want"] for e in s["entries"])}
+    got = helpers.collect_logits(steps, outputs)
+    for rid, toks in requests.items():
+        want = plain.forward(weights, config, toks)
+        rows = torch.stack([got[rid][p] for p in range(len(toks))]).double()
+        bad, rms_err, top_err = helpers.first_wrong_row(rows, want, TOL["float32"])
+        assert bad is None, (rid, bad, rms_err, top_err)
+
+
+SORULIX_C = {
+    "architecture": "Sorulix", "vocab": 211, "width": 256, "norm": {"eps": 1e-6}, "loop": {"start": 0, "stop": 2, "times": 2},
+    "layers": [
+        {"type": "parallel", "mixer": {
+            "left": {"heads": 4, "kv_heads": 2, "dim": 64, "vdim": 64, "scale": 0.125, "softcap": 30.0, "q_temp": {"coef": 0.3, "every": 64}},
+            "right": {"heads": 2, "dim": 64, "vdim": 128, "decay": [0.98, 0.9]}},
+         "mlp": {"kind": "dense", "ff": 512, "limit": 3.0}},
+        {"type": "channel_delta", "mixer": {"heads": 4, "kv_heads": 4, "dim": 64, "vdim": 64, "conv": 4},
+         "mlp": {"kind": "dense", "ff": 512, "limit": 3.0}},
+    ],
+}
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_long_portions_on_the_kernels_of_real_sizes(dtype, tmp_path):
+    """Head size 64, width 256 and portions of 128 tokens and more: in bfloat16 the tcgen05 projections and the
+    tcgen05 attention with rules are on the path, the scans spread a column over 16 lanes; whole prompts, portions
+    of 128 to 200 tokens, and the last tokens one by one."""
+
+    path, weights = helpers.make_sorulix_dir(tmp_path / "c", SORULIX_C, {1: (16, 16)}, 21, torch_dtype=dtype, gain=2.0)
+    from llm_runtime_study_b200.engine.runtime import load
+
+    rng = random.Random(4)
+    requests = {"a": helpers.random_tokens(rng, 211, 333), "b": helpers.random_tokens(rng, 211, 150)}
+    store = plain.round_bfloat16 if dtype == "bfloat16" else plain.keep
+    setup = dict(dtype=dtype, page=16, requests=requests, loaded=load(path, device=DEV, dtype=dtype, strict_dtype=False),
+                 plain={rid: plain.forward(weights, SORULIX_C, tokens, store=store) for rid, tokens in requests.items()})
+    _compare(setup, _replay(setup, helpers.trace_whole(requests)))
+    steps = helpers.trace_chunked(requests, rng, sizes=(128, 130, 200))
+    _compare(setup, _replay(setup, steps))
+    _compare(setup, _replay(setup, helpers.trace_decode_tail(requests, tail=20)))

@@ -600,8 +600,8 @@ def run_sorulix(args) -> dict:
 
         batches = (1, 8, 32)
         engine = Engine.from_random_weights(
-            cfg, seed=0, device="cuda:0", dtype="bfloat16", max_seq_len=8192, max_batch_size=max(batches), page_size=PAGE_SIZE,
-            max_cache_tokens=max(batches) * (context + args.steps + 64), max_tokens_per_step=prefill_tokens, use_cuda_graph=True)
+            cfg, seed=0, device="cuda:0", dtype="bfloat16", max_seq_len=8192, max_batch_size=max(*batches, args.batch), page_size=PAGE_SIZE,
+            max_cache_tokens=max(*batches, args.batch) * (context + args.steps + 64), max_tokens_per_step=prefill_tokens, use_cuda_graph=True)
         runner, manager, sampler = engine.runner, engine.cache_manager, engine._sampler
         prompt = ids(prefill_tokens)
 
@@ -610,11 +610,13 @@ def run_sorulix(args) -> dict:
             runner.step_sampled([StepEntry(request, prompt, [prefill_tokens - 1], greedy)], sampler).tokens()
             manager.release(request)
 
-        for _ in range(3):
-            one_prefill()
-        out = {"prefill_tokens": prefill_tokens, "prefill_ms": round(statistics.median(timed(one_prefill, 1) for _ in range(5)), 3)}
-        out["prefill_tok_s"] = round(prefill_tokens / out["prefill_ms"] * 1e3)
-        for batch in batches:
+        out = {}
+        if args.only != "decode":
+            for _ in range(3):
+                one_prefill()
+            out = {"prefill_tokens": prefill_tokens, "prefill_ms": round(statistics.median(timed(one_prefill, 1) for _ in range(5)), 3)}
+            out["prefill_tok_s"] = round(prefill_tokens / out["prefill_ms"] * 1e3)
+        for batch in (() if args.only == "prefill" else (args.batch,) if args.only == "decode" else batches):
             requests = [manager.admit() for _ in range(batch)]
             for request in requests:
                 runner.step_sampled([StepEntry(request, ids(context), [context - 1], greedy)], sampler)
@@ -638,8 +640,9 @@ def run_sorulix(args) -> dict:
     for name in (() if args.only == "kernels" else args.size.split(",") if args.size else SORULIX_SIZES):
         shape = SORULIX_SIZES[name]
         results[name] = {"shape": dict(zip(("width", "ff", "heads", "kv_heads", "head_dim", "layer_pairs", "vocab"), shape)),
-                         "sorulix": measure(_sorulix_config(*shape), shape[-1]),
-                         "qwen3_equal_size": measure(_qwen3_like(*shape), shape[-1])}
+                         "sorulix": measure(_sorulix_config(*shape), shape[-1])}
+        if args.only not in ("prefill", "decode"):      # those two are profiling aids: the new design alone
+            results[name]["qwen3_equal_size"] = measure(_qwen3_like(*shape), shape[-1])
     kernels = _sorulix_kernels(peak, timed) if args.only in ("all", "kernels") else {}
     return {"workload": "sorulix", "context": context, "steps": args.steps, "warmup": max(args.warmup, 3), "dtype": "bfloat16",
             "data": "synthetic token ids, seeded random weights", "peaks": peak, "models": results, "kernels": kernels}

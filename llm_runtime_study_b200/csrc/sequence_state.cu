@@ -17,6 +17,12 @@ namespace b200 {
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
 __device__ __forceinline__ float silu_f(float x) { return x * sigmoid_f(x); }
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+// SiLU of a value that was stored in 16 bits: the hardware's exponential and reciprocal are exact far beyond the
+// 8 bits of such a value; 32-bit inputs take the full-precision functions.
+template <typename T> __device__ __forceinline__ float silu_of(float x) {
+  if constexpr (sizeof(T) == 2) return __fdividef(x, 1.f + __expf(-x));
+  else return silu_f(x);
+}
 
 // ---------------------------------------------------------------------------- linear scan
 struct ScanParams {
@@ -108,15 +114,15 @@ __global__ void __launch_bounds__(kScanThreads) linear_scan_kernel(const ScanPar
     for (int e = 0; e < EPT; ++e) {
       if (e * kScanThreads >= count * dp) break;
       const int idx = threadIdx.x + e * kScanThreads;
-      ks[idx] = p.act ? silu_f(rk[e]) : rk[e];
-      qs[idx] = p.act ? silu_f(rq[e]) : rq[e];
+      ks[idx] = p.act ? silu_of<T>(rk[e]) : rk[e];
+      qs[idx] = p.act ? silu_of<T>(rq[e]) : rq[e];
       if (GATED) gs[idx] = rg[e];
     }
 #pragma unroll
     for (int e = 0; e < VPT; ++e) {
       if (e * kScanThreads >= count * cols) break;
       const int idx = threadIdx.x + e * kScanThreads;
-      if (idx < CHUNK * cols) vs[idx] = p.act ? silu_f(rv[e]) : rv[e];
+      if (idx < CHUNK * cols) vs[idx] = p.act ? silu_of<T>(rv[e]) : rv[e];
     }
     if (DELTA && threadIdx.x < CHUNK) bs[threadIdx.x] = rb;
   };
@@ -217,7 +223,7 @@ struct DeltaPrepareParams {
   const float* conv_state;         // [slots, ntaps - 1, C]: inputs of the positions before this step, oldest first
   const float* a_log;              // [H]
   const float* dt_bias;            // [H d]
-  const void* a_up;                // [H d, rank] storage type
+  const void* a_up;                // [rank, H d] storage type (the map's weight transposed: neighbouring threads read neighbouring outputs)
   float* q; float* k; float* v; float* g; float* beta;   // [n, G d], [n, G d], [n, H dv], [n, H d], [n, H]
   const int* q_start; const int* slots; const int* token_entry;
   int H, G, d, dv;
@@ -270,7 +276,7 @@ __global__ void __launch_bounds__(256) delta_prepare_kernel(const DeltaPreparePa
   const T* up = static_cast<const T*>(p.a_up);
   for (int i = threadIdx.x; i < hd; i += blockDim.x) {
     float a = 0.f;
-    for (int j = 0; j < p.rank; ++j) a = fmaf(to_float(up[static_cast<size_t>(i) * p.rank + j]), low[j], a);
+    for (int j = 0; j < p.rank; ++j) a = fmaf(to_float(up[static_cast<size_t>(j) * hd + i]), low[j], a);
     const float rate = expf(p.a_log[i / p.d]);
     p.g[static_cast<size_t>(t) * hd + i] = expf(-rate * softplus_f(a + p.dt_bias[i]));
   }
@@ -298,7 +304,8 @@ __global__ void conv_state_update_kernel(const T* __restrict__ proj, int ld, flo
 
 // ------------------------------------------------------------- group norm times sigmoid gate
 // out[t, c] = x[t, c] * rsqrt(mean over c's group of x^2 + eps) * w[c % group] * sigmoid(gate[t, c]);
-// the gate's logits are read from `gate_in` directly (rank 0) or formed as gate_up[c, :] . gate_in[t, :rank].
+// the gate's logits are read from `gate_in` directly (rank 0) or formed as gate_up[:, c] . gate_in[t, :rank]
+// (gate_up is [rank, width]: the map's weight transposed).
 template <typename T>
 __global__ void group_norm_gate_kernel(const float* __restrict__ x, int width, int group, const float* __restrict__ w, float eps,
                                        const T* __restrict__ gate_in, int gate_ld, int rank, const T* __restrict__ gate_up,
@@ -320,7 +327,7 @@ __global__ void group_norm_gate_kernel(const float* __restrict__ x, int width, i
       logit = to_float(gate_in[static_cast<size_t>(t) * gate_ld + c]);
     } else {
       logit = 0.f;
-      for (int j = 0; j < rank; ++j) logit = fmaf(to_float(gate_up[static_cast<size_t>(c) * rank + j]), low[j], logit);
+      for (int j = 0; j < rank; ++j) logit = fmaf(to_float(gate_up[static_cast<size_t>(j) * width + c]), low[j], logit);
     }
     out[static_cast<size_t>(t) * width + c] = from_float<T>(row[i] * f * w[i] * sigmoid_f(logit));
   }

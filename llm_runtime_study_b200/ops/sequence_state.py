@@ -57,7 +57,8 @@ def delta_prepare(
     """From one stacked projection ``[N, q | k | v | ...]``: the short convolution over time and SiLU of every q, k
     and v channel (inputs before the step come from ``conv_state`` ``[slots, taps-1, channels]``), each q and k head
     divided by ``sqrt(sum of squares + unit_eps)`` (q times ``q_scale``), ``beta = sigmoid(proj[:, beta_offset + h])``
-    and the decay factors ``exp(-exp(a_log[h]) * softplus(a_up @ proj[:, low_offset : low_offset + rank] + dt_bias))``.
+    and the decay factors ``exp(-exp(a_log[h]) * softplus(proj[:, low_offset : low_offset + rank] @ a_up + dt_bias))``
+    (``a_up`` is ``[rank, heads * dim]``: the map's weight transposed, so that neighbouring threads read neighbouring outputs).
     Returns float32 ``(q, k, v, g, beta)``."""
 
     require(proj, "proj", dims=2)
@@ -72,7 +73,7 @@ def delta_prepare(
         raise KernelError(f"conv_state has shape {tuple(conv_state.shape)}, expected [slots, {ntaps - 1}, {channels}]")
     require(a_log, "a_log", dtype=torch.float32, shape=(heads,))
     require(dt_bias, "dt_bias", dtype=torch.float32, shape=(heads * dim,))
-    require(a_up, "a_up", dtype=proj.dtype, shape=(heads * dim, rank))
+    require(a_up, "a_up", dtype=proj.dtype, shape=(rank, heads * dim))
     if max(beta_offset + heads, low_offset + rank, channels) > ld:
         raise KernelError("delta_prepare: a column block lies outside the projection")
     dev = proj.device
@@ -102,7 +103,8 @@ def group_norm_gate(x: torch.Tensor, weight: torch.Tensor, eps: float, gate_in: 
                     gate_up: torch.Tensor | None = None, out_dtype: torch.dtype) -> torch.Tensor:
     """``x`` float32 ``[N, width]`` in groups of ``len(weight)`` columns: each group divided by its root mean square,
     times ``weight``, times ``sigmoid(logit)``; the logits are columns ``gate_offset ..`` of ``gate_in`` (``width`` of
-    them), or, with ``gate_up`` ``[width, rank]``, ``gate_up @ gate_in[:, gate_offset : gate_offset + rank]``."""
+    them), or, with ``gate_up`` ``[rank, width]`` (a low-rank map's weight transposed),
+    ``gate_in[:, gate_offset : gate_offset + rank] @ gate_up``."""
 
     require(x, "x", dtype=torch.float32, dims=2)
     n, width = x.shape
@@ -114,9 +116,9 @@ def group_norm_gate(x: torch.Tensor, weight: torch.Tensor, eps: float, gate_in: 
     rank = 0
     if gate_up is not None:
         require(gate_up, "gate_up", dtype=out_dtype, dims=2)
-        rank = gate_up.shape[1]
-        if gate_up.shape[0] != width:
-            raise KernelError(f"gate_up has {gate_up.shape[0]} rows, expected {width}")
+        rank = gate_up.shape[0]
+        if gate_up.shape[1] != width:
+            raise KernelError(f"gate_up has {gate_up.shape[1]} columns, expected {width}")
     if gate_offset + (rank or width) > gate_in.shape[1]:
         raise KernelError("group_norm_gate: the gate's columns lie outside gate_in")
     out = torch.empty((n, width), dtype=out_dtype, device=x.device)

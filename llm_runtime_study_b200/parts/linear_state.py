@@ -121,8 +121,9 @@ class GatedDeltaRule(Mixer):
         self.conv_taps = torch.cat([runtime.place_vector_f32(tensors[f"{n}.conv"]) for n in ("q", "k", "v")], dim=0)
         self.a_log = runtime.place_vector_f32(tensors["A_log"])
         self.dt_bias = runtime.place_vector_f32(tensors["dt_bias"])
-        self.a_up = runtime.place_matrix(tensors["a2"])
-        self.g_up = runtime.place_matrix(tensors["g2"])
+        # the second halves of the low-rank maps are applied inside the kernels, which read them transposed
+        self.a_up = runtime.place_matrix(tensors["a2"]).t().contiguous()
+        self.g_up = runtime.place_matrix(tensors["g2"]).t().contiguous()
         self.norm_weight = runtime.place_vector_f32(tensors["norm"])
 
     def cache_requirement(self):

@@ -297,7 +297,7 @@ def test_convolution_unit_norm_and_decay_across_cuts(taps, cuts):
         entry = torch.zeros(m, dtype=torch.int32, device=DEV)
         outs.append([t.cpu() for t in S.delta_prepare(
             part, heads=heads, qk_heads=qk_heads, dim=d, vdim=dv, beta_offset=channels, low_offset=channels + heads, rank=rank,
-            taps=w.to(DEV), conv_state=conv_state, a_log=a_log.to(DEV), dt_bias=dt_bias.to(DEV), a_up=a_up.to(DEV),
+            taps=w.to(DEV), conv_state=conv_state, a_log=a_log.to(DEV), dt_bias=dt_bias.to(DEV), a_up=a_up.t().contiguous().to(DEV),
             q_start=q_start, slots=slot, token_entry=entry, unit_eps=1e-6, q_scale=d ** -0.5)])
         if taps > 1:
             S.conv_state_update(part, conv_state, q_start, slot)
@@ -338,7 +338,7 @@ def test_small_kernels_against_plain():
     assert (dev.cpu() - (resid + a + w1)).abs().max() < 1e-6
     # group norm with a low-rank gate, and with the gate's logits given directly
     o, gate_in, up, w = torch.randn(6, 4 * 24), torch.randn(6, 11), torch.randn(4 * 24, 3), torch.randn(24)
-    got = S.group_norm_gate(o.to(DEV), w.to(DEV), 1e-5, gate_in.to(DEV), gate_offset=8, gate_up=up.to(DEV), out_dtype=torch.float32).cpu().double()
+    got = S.group_norm_gate(o.to(DEV), w.to(DEV), 1e-5, gate_in.to(DEV), gate_offset=8, gate_up=up.t().contiguous().to(DEV), out_dtype=torch.float32).cpu().double()
     want = plain.norm_plain(o.double().view(6, 4, 24), w.double(), 1e-5).reshape(6, -1) * plain.sigmoid(gate_in[:, 8:].double() @ up.double().T)
     assert (got - want).abs().max() < 1e-5
     logits = torch.randn(6, 100)

@@ -792,15 +792,35 @@ __global__ void glu_limit_vec_kernel(const T* __restrict__ gate_up, T* __restric
   *reinterpret_cast<V*>(out + static_cast<size_t>(blockIdx.y) * inter + i) = Vec<T>::pack(y);
 }
 
-// out[t] (+)= factor * x[t] * rsqrt(mean(x[t]^2) + eps) * w
+// out[t] (+)= factor * x[t] * rsqrt(mean(x[t]^2) + eps) * w.  With `cached` the row is kept in shared memory
+// between the two passes (16-byte accesses; the width is then a multiple of 4 and the rows start on 16 bytes).
 __global__ void rmsnorm_accumulate_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ out,
-                                          int hidden, float eps, float factor, int accumulate) {
+                                          int hidden, float eps, float factor, int accumulate, int cached) {
   __shared__ float scratch[32];
+  extern __shared__ __align__(16) float kept[];
   pdl_trigger();
   pdl_wait();
   const float* row = x + static_cast<size_t>(blockIdx.x) * hidden;
   float* dst = out + static_cast<size_t>(blockIdx.x) * hidden;
   float ss = 0.f;
+  if (cached) {
+    for (int i = threadIdx.x; i < hidden / 4; i += blockDim.x) {
+      const float4 v = reinterpret_cast<const float4*>(row)[i];
+      reinterpret_cast<float4*>(kept)[i] = v;
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    const float f = rsqrtf(block_sum(ss, scratch) / static_cast<float>(hidden) + eps) * factor;
+    for (int i = threadIdx.x; i < hidden / 4; i += blockDim.x) {
+      const float4 v = reinterpret_cast<const float4*>(kept)[i], g = reinterpret_cast<const float4*>(w)[i];
+      float4 y = make_float4(v.x * f * g.x, v.y * f * g.y, v.z * f * g.z, v.w * f * g.w);
+      if (accumulate) {
+        const float4 o = reinterpret_cast<const float4*>(dst)[i];
+        y.x += o.x; y.y += o.y; y.z += o.z; y.w += o.w;
+      }
+      reinterpret_cast<float4*>(dst)[i] = y;
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) ss = fmaf(row[i], row[i], ss);
   const float f = rsqrtf(block_sum(ss, scratch) / static_cast<float>(hidden) + eps) * factor;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
@@ -863,7 +883,10 @@ extern "C" int b200_rmsnorm_accumulate(const float* x, const float* w, float* ou
   using namespace b200;
   if (n <= 0) return 0;
   if (hidden <= 0) return B200_ERR_BAD_SIZE;
-  launch(rmsnorm_accumulate_kernel, dim3(n), dim3(256), 0, stream, x, w, out, hidden, eps, factor, accumulate);
+  const bool cached = hidden % 4 == 0 && hidden <= 12288 &&
+                      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  launch(rmsnorm_accumulate_kernel, dim3(n), dim3(256), cached ? sizeof(float) * hidden : 0, stream, x, w, out, hidden, eps, factor,
+         accumulate, cached ? 1 : 0);
   return launch_status();
 }
 

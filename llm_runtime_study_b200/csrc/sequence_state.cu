@@ -85,18 +85,21 @@ __global__ void __launch_bounds__(kScanThreads) linear_scan_kernel(const ScanPar
 
   // The rows of the next chunk are asked for before the tokens of this one are worked through, and land in
   // registers; they go to shared memory (SiLU applied once per element) when this chunk is done.
-  float rk[EPT], rq[EPT], rg[EPT], rv[VPT], rb = 0.f;
+  // (kept in the storage type: a conversion right behind the load would wait for it)
+  T rk[EPT], rq[EPT], rv[VPT];
+  float rg[EPT], rb = 0.f;
   auto fetch = [&](int t0, int count) {
 #pragma unroll
     for (int e = 0; e < EPT; ++e) {
       if (e * kScanThreads >= count * dp) break;       // a single decoded token fills one round, not sixteen
       const int idx = threadIdx.x + e * kScanThreads;
       const int tt = idx / dp, i = idx % dp;
-      rk[e] = rq[e] = rg[e] = 0.f;
+      rk[e] = rq[e] = from_float<T>(0.f);
+      rg[e] = 0.f;
       if (tt < count && i < d) {
         const size_t row = static_cast<size_t>(t0 + tt);
-        rk[e] = to_float(kg[row * p.ldk + hqk * d + i]);
-        rq[e] = to_float(qg[row * p.ldq + hqk * d + i]);
+        rk[e] = kg[row * p.ldk + hqk * d + i];
+        rq[e] = qg[row * p.ldq + hqk * d + i];
         if (GATED) rg[e] = p.gate[row * p.ldg + h * d + i];
       }
     }
@@ -105,7 +108,7 @@ __global__ void __launch_bounds__(kScanThreads) linear_scan_kernel(const ScanPar
       if (e * kScanThreads >= count * cols) break;
       const int idx = threadIdx.x + e * kScanThreads;
       const int tt = idx / cols, c = cb * cols + idx % cols;
-      rv[e] = (tt < count && c < dv) ? to_float(vg[static_cast<size_t>(t0 + tt) * p.ldv + h * dv + c]) : 0.f;
+      rv[e] = (tt < count && c < dv) ? vg[static_cast<size_t>(t0 + tt) * p.ldv + h * dv + c] : from_float<T>(0.f);
     }
     if (DELTA && threadIdx.x < count) rb = p.beta[static_cast<size_t>(t0 + threadIdx.x) * p.ldb + h];
   };
@@ -114,15 +117,15 @@ __global__ void __launch_bounds__(kScanThreads) linear_scan_kernel(const ScanPar
     for (int e = 0; e < EPT; ++e) {
       if (e * kScanThreads >= count * dp) break;
       const int idx = threadIdx.x + e * kScanThreads;
-      ks[idx] = p.act ? silu_of<T>(rk[e]) : rk[e];
-      qs[idx] = p.act ? silu_of<T>(rq[e]) : rq[e];
+      ks[idx] = p.act ? silu_of<T>(to_float(rk[e])) : to_float(rk[e]);
+      qs[idx] = p.act ? silu_of<T>(to_float(rq[e])) : to_float(rq[e]);
       if (GATED) gs[idx] = rg[e];
     }
 #pragma unroll
     for (int e = 0; e < VPT; ++e) {
       if (e * kScanThreads >= count * cols) break;
       const int idx = threadIdx.x + e * kScanThreads;
-      if (idx < CHUNK * cols) vs[idx] = p.act ? silu_of<T>(rv[e]) : rv[e];
+      if (idx < CHUNK * cols) vs[idx] = p.act ? silu_of<T>(to_float(rv[e])) : to_float(rv[e]);
     }
     if (DELTA && threadIdx.x < CHUNK) bs[threadIdx.x] = rb;
   };
@@ -230,55 +233,66 @@ struct DeltaPrepareParams {
   float unit_eps, q_scale;
 };
 
-// One CTA per token: convolution and SiLU of every channel, unit norm of each q and k head, the
-// decay factors g = exp(-exp(a_log) * softplus(low-rank(x) + dt_bias)), and beta = sigmoid(.).
+// One CTA per token and head: the convolution and SiLU of the head's value channels, of its q and k channels
+// (the first head of a group of heads that share them does these), their unit norms, the head's decay factors
+// g = exp(-exp(a_log) * softplus(low-rank(x) + dt_bias)), and beta = sigmoid(.).  Every sum has an order that
+// depends on the sizes only.
 template <typename T>
-__global__ void __launch_bounds__(256) delta_prepare_kernel(const DeltaPrepareParams p) {
+__global__ void __launch_bounds__(128) delta_prepare_kernel(const DeltaPrepareParams p) {
   extern __shared__ float smem[];
+  __shared__ float scratch[32];
   pdl_trigger();
   pdl_wait();
-  const int t = blockIdx.x;
+  const int t = blockIdx.x, h = blockIdx.y;
   const int entry = p.token_entry[t];
   const int first = p.q_start[entry];
   const int local = t - first;
   const int slot = p.slots[entry];
-  const int qk = p.G * p.d, C = 2 * qk + p.H * p.dv, K = p.ntaps;
+  const int d = p.d, dv = p.dv, qk = p.G * d, C = 2 * qk + p.H * dv, K = p.ntaps;
+  const int group = p.H / p.G, gq = h / group;
+  const bool does_qk = h % group == 0;
   const T* proj = static_cast<const T*>(p.proj);
-  float* sc = smem;            // [C] channels after convolution and SiLU
-  float* low = smem + C;       // [rank]
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+  float* sq = smem;            // [d]
+  float* sk = smem + d;        // [d]
+  float* low = smem + 2 * d;   // [rank]
+  auto conv = [&](int c) {
     float acc = 0.f;
     for (int j = 0; j < K; ++j) {
-      const int back = K - 1 - j, at = local - back;
+      const int at = local - (K - 1 - j);
       const float x = at >= 0 ? to_float(proj[static_cast<size_t>(first + at) * p.ld + c])
                               : p.conv_state[(static_cast<size_t>(slot) * (K - 1) + (K - 1 + at)) * C + c];
       acc = fmaf(p.taps[static_cast<size_t>(c) * K + j], x, acc);
     }
-    sc[c] = silu_f(acc);
-  }
+    return silu_of<T>(acc);
+  };
   for (int i = threadIdx.x; i < p.rank; i += blockDim.x) low[i] = to_float(proj[static_cast<size_t>(t) * p.ld + p.a_off + i]);
-  __syncthreads();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  for (int head = warp; head < 2 * p.G; head += nwarps) {      // q heads, then k heads
-    const float* x = sc + head * p.d;
-    float ss = 0.f;
-    for (int i = lane; i < p.d; i += 32) ss = fmaf(x[i], x[i], ss);
-    ss = warp_sum(ss);
-    const bool is_q = head < p.G;
-    const float f = rsqrtf(ss + p.unit_eps) * (is_q ? p.q_scale : 1.f);
-    float* dst = (is_q ? p.q : p.k) + static_cast<size_t>(t) * qk + (is_q ? head : head - p.G) * p.d;
-    for (int i = lane; i < p.d; i += 32) dst[i] = x[i] * f;
+  const size_t hv = static_cast<size_t>(p.H) * dv, hd = static_cast<size_t>(p.H) * d;
+  for (int i = threadIdx.x; i < dv; i += blockDim.x) p.v[t * hv + h * dv + i] = conv(2 * qk + h * dv + i);
+  if (does_qk) {               // the same for every thread of the CTA
+    float ssq = 0.f, ssk = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+      const float a = conv(gq * d + i), b = conv(qk + gq * d + i);
+      sq[i] = a;
+      sk[i] = b;
+      ssq = fmaf(a, a, ssq);
+      ssk = fmaf(b, b, ssk);
+    }
+    const float fq = rsqrtf(block_sum(ssq, scratch) + p.unit_eps) * p.q_scale;
+    const float fk = rsqrtf(block_sum(ssk, scratch) + p.unit_eps);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+      p.q[static_cast<size_t>(t) * qk + gq * d + i] = sq[i] * fq;
+      p.k[static_cast<size_t>(t) * qk + gq * d + i] = sk[i] * fk;
+    }
   }
-  const int hv = p.H * p.dv, hd = p.H * p.d;
-  for (int i = threadIdx.x; i < hv; i += blockDim.x) p.v[static_cast<size_t>(t) * hv + i] = sc[2 * qk + i];
-  for (int h = threadIdx.x; h < p.H; h += blockDim.x)
-    p.beta[static_cast<size_t>(t) * p.H + h] = sigmoid_f(to_float(proj[static_cast<size_t>(t) * p.ld + p.b_off + h]));
+  __syncthreads();             // low[] is complete
+  if (threadIdx.x == 0) p.beta[static_cast<size_t>(t) * p.H + h] = sigmoid_f(to_float(proj[static_cast<size_t>(t) * p.ld + p.b_off + h]));
   const T* up = static_cast<const T*>(p.a_up);
-  for (int i = threadIdx.x; i < hd; i += blockDim.x) {
+  const float rate = expf(p.a_log[h]);
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const size_t col = static_cast<size_t>(h) * d + i;
     float a = 0.f;
-    for (int j = 0; j < p.rank; ++j) a = fmaf(to_float(up[static_cast<size_t>(j) * hd + i]), low[j], a);
-    const float rate = expf(p.a_log[i / p.d]);
-    p.g[static_cast<size_t>(t) * hd + i] = expf(-rate * softplus_f(a + p.dt_bias[i]));
+    for (int j = 0; j < p.rank; ++j) a = fmaf(to_float(up[static_cast<size_t>(j) * hd + col]), low[j], a);
+    p.g[t * hd + col] = expf(-rate * softplus_f(a + p.dt_bias[col]));
   }
 }
 
@@ -372,19 +386,9 @@ extern "C" int b200_delta_prepare(const void* proj, int ld, int b_off, int a_off
   if (H <= 0 || G <= 0 || H % G != 0 || d <= 0 || dv <= 0 || ntaps <= 0 || rank < 0) return B200_ERR_BAD_SIZE;
   DeltaPrepareParams p{proj, ld, b_off, a_off, rank, taps, ntaps, conv_state, a_log, dt_bias, a_up, q, k, v, g, beta,
                        q_start, slots, token_entry, H, G, d, dv, unit_eps, q_scale};
-  const size_t smem = sizeof(float) * (static_cast<size_t>(2) * G * d + static_cast<size_t>(H) * dv + rank);
-  // the opt-in to large shared memory is made once per device, for the largest row this kernel takes
-  static DeviceOnce once_f32, once_bf16;
-  if (smem > 200 * 1024) return B200_ERR_TOO_LARGE;
-  if (dtype == kF32) {
-    if (int e = configure_once(once_f32, delta_prepare_kernel<float>, 200 * 1024)) return e;
-    launch(delta_prepare_kernel<float>, dim3(n), dim3(256), smem, stream, p);
-  } else if (dtype == kBF16) {
-    if (int e = configure_once(once_bf16, delta_prepare_kernel<__nv_bfloat16>, 200 * 1024)) return e;
-    launch(delta_prepare_kernel<__nv_bfloat16>, dim3(n), dim3(256), smem, stream, p);
-  } else {
-    return B200_ERR_BAD_DTYPE;
-  }
+  const size_t smem = sizeof(float) * (static_cast<size_t>(2) * d + rank);
+  if (smem > 48 * 1024 || H > 65535) return B200_ERR_TOO_LARGE;
+  B200_DISPATCH_DTYPE(dtype, T, launch(delta_prepare_kernel<T>, dim3(n, H), dim3(128), smem, stream, p));
   return launch_status();
 }
 

@@ -233,66 +233,81 @@ struct DeltaPrepareParams {
   float unit_eps, q_scale;
 };
 
-// One CTA per token and head: the convolution and SiLU of the head's value channels, of its q and k channels
-// (the first head of a group of heads that share them does these), their unit norms, the head's decay factors
-// g = exp(-exp(a_log) * softplus(low-rank(x) + dt_bias)), and beta = sigmoid(.).  Every sum has an order that
-// depends on the sizes only.
+// One CTA per head and block of `tokens_per_cta` tokens (1 for small batches, so that a decode step spreads over
+// heads x tokens CTAs; more for prompt portions, so that the head's taps and its slice of the low-rank map are
+// fetched once per CTA into shared memory).  Per token: the convolution and SiLU of the head's value channels, of its
+// q and k channels (the first head of a group of heads that share them does these), their unit norms, the head's
+// decay factors g = exp(-exp(a_log) * softplus(low-rank(x) + dt_bias)), and beta = sigmoid(.).  Every sum has an
+// order that depends on the sizes only.
 template <typename T>
-__global__ void __launch_bounds__(128) delta_prepare_kernel(const DeltaPrepareParams p) {
+__global__ void __launch_bounds__(128) delta_prepare_kernel(const DeltaPrepareParams p, int n, int tokens_per_cta) {
   extern __shared__ float smem[];
   __shared__ float scratch[32];
   pdl_trigger();
   pdl_wait();
-  const int t = blockIdx.x, h = blockIdx.y;
-  const int entry = p.token_entry[t];
-  const int first = p.q_start[entry];
-  const int local = t - first;
-  const int slot = p.slots[entry];
+  const int h = blockIdx.y;
   const int d = p.d, dv = p.dv, qk = p.G * d, C = 2 * qk + p.H * dv, K = p.ntaps;
   const int group = p.H / p.G, gq = h / group;
   const bool does_qk = h % group == 0;
   const T* proj = static_cast<const T*>(p.proj);
-  float* sq = smem;            // [d]
-  float* sk = smem + d;        // [d]
-  float* low = smem + 2 * d;   // [rank]
-  auto conv = [&](int c) {
-    float acc = 0.f;
-    for (int j = 0; j < K; ++j) {
-      const int at = local - (K - 1 - j);
-      const float x = at >= 0 ? to_float(proj[static_cast<size_t>(first + at) * p.ld + c])
-                              : p.conv_state[(static_cast<size_t>(slot) * (K - 1) + (K - 1 + at)) * C + c];
-      acc = fmaf(p.taps[static_cast<size_t>(c) * K + j], x, acc);
-    }
-    return silu_of<T>(acc);
-  };
-  for (int i = threadIdx.x; i < p.rank; i += blockDim.x) low[i] = to_float(proj[static_cast<size_t>(t) * p.ld + p.a_off + i]);
   const size_t hv = static_cast<size_t>(p.H) * dv, hd = static_cast<size_t>(p.H) * d;
-  for (int i = threadIdx.x; i < dv; i += blockDim.x) p.v[t * hv + h * dv + i] = conv(2 * qk + h * dv + i);
-  if (does_qk) {               // the same for every thread of the CTA
-    float ssq = 0.f, ssk = 0.f;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
-      const float a = conv(gq * d + i), b = conv(qk + gq * d + i);
-      sq[i] = a;
-      sk[i] = b;
-      ssq = fmaf(a, a, ssq);
-      ssk = fmaf(b, b, ssk);
-    }
-    const float fq = rsqrtf(block_sum(ssq, scratch) + p.unit_eps) * p.q_scale;
-    const float fk = rsqrtf(block_sum(ssk, scratch) + p.unit_eps);
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
-      p.q[static_cast<size_t>(t) * qk + gq * d + i] = sq[i] * fq;
-      p.k[static_cast<size_t>(t) * qk + gq * d + i] = sk[i] * fk;
-    }
-  }
-  __syncthreads();             // low[] is complete
-  if (threadIdx.x == 0) p.beta[static_cast<size_t>(t) * p.H + h] = sigmoid_f(to_float(proj[static_cast<size_t>(t) * p.ld + p.b_off + h]));
+  float* sq = smem;                    // [d]
+  float* sk = sq + d;                  // [d]
+  float* low = sk + d;                 // [rank]
+  float* up_s = low + p.rank;          // [rank][d]: this head's slice of the low-rank map
+  float* taps_s = up_s + p.rank * d;   // [(2 d + dv)][K]: taps of this head's q, k and v channels
   const T* up = static_cast<const T*>(p.a_up);
+  for (int idx = threadIdx.x; idx < p.rank * d; idx += blockDim.x)
+    up_s[idx] = to_float(up[static_cast<size_t>(idx / d) * hd + static_cast<size_t>(h) * d + idx % d]);
+  for (int idx = threadIdx.x; idx < (2 * d + dv) * K; idx += blockDim.x) {
+    const int lc = idx / K, j = idx % K;     // local channel: q [0, d), k [d, 2d), v [2d, 2d + dv)
+    const int c = lc < d ? gq * d + lc : (lc < 2 * d ? qk + gq * d + (lc - d) : 2 * qk + h * dv + (lc - 2 * d));
+    taps_s[idx] = p.taps[static_cast<size_t>(c) * K + j];
+  }
   const float rate = expf(p.a_log[h]);
-  for (int i = threadIdx.x; i < d; i += blockDim.x) {
-    const size_t col = static_cast<size_t>(h) * d + i;
-    float a = 0.f;
-    for (int j = 0; j < p.rank; ++j) a = fmaf(to_float(up[static_cast<size_t>(j) * hd + col]), low[j], a);
-    p.g[t * hd + col] = expf(-rate * softplus_f(a + p.dt_bias[col]));
+  const int t_end = min(n, (static_cast<int>(blockIdx.x) + 1) * tokens_per_cta);
+  for (int t = blockIdx.x * tokens_per_cta; t < t_end; ++t) {
+    const int entry = p.token_entry[t];
+    const int first = p.q_start[entry];
+    const int local = t - first;
+    const int slot = p.slots[entry];
+    auto conv = [&](int c, int lc) {
+      float acc = 0.f;
+      for (int j = 0; j < K; ++j) {
+        const int at = local - (K - 1 - j);
+        const float x = at >= 0 ? to_float(proj[static_cast<size_t>(first + at) * p.ld + c])
+                                : p.conv_state[(static_cast<size_t>(slot) * (K - 1) + (K - 1 + at)) * C + c];
+        acc = fmaf(taps_s[lc * K + j], x, acc);
+      }
+      return silu_of<T>(acc);
+    };
+    __syncthreads();             // the shared arrays are filled, and the token before is done with sq, sk and low
+    for (int i = threadIdx.x; i < p.rank; i += blockDim.x) low[i] = to_float(proj[static_cast<size_t>(t) * p.ld + p.a_off + i]);
+    for (int i = threadIdx.x; i < dv; i += blockDim.x) p.v[t * hv + h * dv + i] = conv(2 * qk + h * dv + i, 2 * d + i);
+    if (does_qk) {               // the same for every thread of the CTA
+      float ssq = 0.f, ssk = 0.f;
+      for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float a = conv(gq * d + i, i), b = conv(qk + gq * d + i, d + i);
+        sq[i] = a;
+        sk[i] = b;
+        ssq = fmaf(a, a, ssq);
+        ssk = fmaf(b, b, ssk);
+      }
+      const float fq = rsqrtf(block_sum(ssq, scratch) + p.unit_eps) * p.q_scale;
+      const float fk = rsqrtf(block_sum(ssk, scratch) + p.unit_eps);
+      for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        p.q[static_cast<size_t>(t) * qk + gq * d + i] = sq[i] * fq;
+        p.k[static_cast<size_t>(t) * qk + gq * d + i] = sk[i] * fk;
+      }
+    }
+    __syncthreads();             // low[] is complete
+    if (threadIdx.x == 0) p.beta[static_cast<size_t>(t) * p.H + h] = sigmoid_f(to_float(proj[static_cast<size_t>(t) * p.ld + p.b_off + h]));
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+      const size_t col = static_cast<size_t>(h) * d + i;
+      float a = 0.f;
+      for (int j = 0; j < p.rank; ++j) a = fmaf(up_s[j * d + i], low[j], a);
+      p.g[t * hd + col] = expf(-rate * softplus_f(a + p.dt_bias[col]));
+    }
   }
 }
 
@@ -386,9 +401,21 @@ extern "C" int b200_delta_prepare(const void* proj, int ld, int b_off, int a_off
   if (H <= 0 || G <= 0 || H % G != 0 || d <= 0 || dv <= 0 || ntaps <= 0 || rank < 0) return B200_ERR_BAD_SIZE;
   DeltaPrepareParams p{proj, ld, b_off, a_off, rank, taps, ntaps, conv_state, a_log, dt_bias, a_up, q, k, v, g, beta,
                        q_start, slots, token_entry, H, G, d, dv, unit_eps, q_scale};
-  const size_t smem = sizeof(float) * (static_cast<size_t>(2) * d + rank);
-  if (smem > 48 * 1024 || H > 65535) return B200_ERR_TOO_LARGE;
-  B200_DISPATCH_DTYPE(dtype, T, launch(delta_prepare_kernel<T>, dim3(n, H), dim3(128), smem, stream, p));
+  const size_t smem = sizeof(float) * (static_cast<size_t>(2) * d + rank + static_cast<size_t>(rank) * d + (static_cast<size_t>(2) * d + dv) * ntaps);
+  if (smem > 200 * 1024 || H > 65535) return B200_ERR_TOO_LARGE;
+  // small batches: a CTA per token and head; prompt portions: eight tokens share a CTA's copy of the head's weights
+  const int tokens_per_cta = n * H >= 8 * 2 * 148 ? 8 : 1;
+  dim3 grid((n + tokens_per_cta - 1) / tokens_per_cta, H);
+  static DeviceOnce once_f32, once_bf16;     // the opt-in to large shared memory is made once per device, for the largest sizes taken
+  if (dtype == kF32) {
+    if (int e = configure_once(once_f32, delta_prepare_kernel<float>, 200 * 1024)) return e;
+    launch(delta_prepare_kernel<float>, grid, dim3(128), smem, stream, p, n, tokens_per_cta);
+  } else if (dtype == kBF16) {
+    if (int e = configure_once(once_bf16, delta_prepare_kernel<__nv_bfloat16>, 200 * 1024)) return e;
+    launch(delta_prepare_kernel<__nv_bfloat16>, grid, dim3(128), smem, stream, p, n, tokens_per_cta);
+  } else {
+    return B200_ERR_BAD_DTYPE;
+  }
   return launch_status();
 }
 

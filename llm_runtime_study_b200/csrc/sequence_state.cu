@@ -1,6 +1,7 @@
 // Mixers that carry a state of fixed size per request instead of a growing cache:
 //
 //   linear scan     S_t = D_t S_(t-1) + k_t u_t^T,  o_t = S_t^T q_t        per head, S is [d, dv]
+//                   (the delta rule's read-out is formed as (D_t S_(t-1))^T q_t + u_t (k_t . q_t), the same sum)
 //                   D_t = one decay per head (a constant), or a diagonal of per-row factors g_t (gated)
 //                   u_t = v_t (plain), or beta_t (v_t - (D_t S_(t-1))^T k_t) (delta rule)
 //   short convolution over time per channel, with the last taps-1 inputs kept per request
@@ -42,16 +43,17 @@ constexpr int kScanThreads = 128;
 constexpr int scan_chunk(int dpt, int rl) { return dpt * rl <= 128 ? 16 : 8; }
 
 // One CTA owns some columns of one head's state for one request.  A column is independent of the
-// others: S[:, c] <- D S[:, c] + k u_c.  Its d rows are spread over RL lanes of one warp (row i
-// belongs to lane i % RL), DPT rows per lane in registers; the two dot products over rows are
-// finished by shuffles.  RL = 4 keeps 8 neighbouring columns (one 32-byte sector of a state row) in
+// others: S[:, c] <- D S[:, c] + k u_c.  Its d rows are spread over RL lanes of one warp (lane r
+// owns rows r * DPT .. r * DPT + DPT - 1, so that it reads its part of k, q and g from shared memory
+// 16 bytes at a time), DPT rows per lane in registers; the two dot products over rows are finished
+// by shuffles.  RL = 4 keeps 8 neighbouring columns (one 32-byte sector of a state row) in
 // a warp, which is what a launch that mostly moves states wants (many requests, one token each);
 // RL = 16 spreads a column over more lanes and a head over sixteen times as many CTAs, which is
 // what a launch with few requests and long portions wants: its time is a chain of dependent steps,
 // and the chain per token is a quarter as long.
 template <typename T, int DPT, int RL, bool DELTA, bool GATED>
 __global__ void __launch_bounds__(kScanThreads) linear_scan_kernel(const ScanParams p) {
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   pdl_trigger();
   pdl_wait();
   constexpr int rl = RL, cols_per_warp = 32 / rl, cols = (kScanThreads / 32) * cols_per_warp;
@@ -134,7 +136,7 @@ __global__ void __launch_bounds__(kScanThreads) linear_scan_kernel(const ScanPar
   float S[DPT];
 #pragma unroll
   for (int ii = 0; ii < DPT; ++ii) {
-    const int i = ii * rl + r;
+    const int i = r * DPT + ii;
     S[ii] = (live && i < d) ? sbase[static_cast<size_t>(i) * dv + col] : 0.f;
   }
 
@@ -145,39 +147,86 @@ __global__ void __launch_bounds__(kScanThreads) linear_scan_kernel(const ScanPar
     __syncthreads();
     if (t0 + CHUNK < t_end) fetch(t0 + CHUNK, min(CHUNK, t_end - t0 - CHUNK));
     for (int tt = 0; tt < count; ++tt) {
-      const float* kt = ks + tt * dp;
-      const float* qt = qs + tt * dp;
-      const float* gt = gs + tt * dp;
-      float dot[4] = {0.f, 0.f, 0.f, 0.f};
+      const float4* kt = reinterpret_cast<const float4*>(ks + tt * dp + r * DPT);
+      const float4* qt = reinterpret_cast<const float4*>(qs + tt * dp + r * DPT);
+      const float4* gt = reinterpret_cast<const float4*>(gs + tt * dp + r * DPT);
+      float4 kk[DPT / 4];
+      float o_sum;
+      if constexpr (DELTA) {
+        // o = (D S)^T q + u (k . q): the three sums over rows (against k, against q, and k . q) are formed in one
+        // pass and reduced over the lanes together, so a token costs one shuffle tree, not two in a row
+        float dot[2] = {0.f, 0.f}, oq[2] = {0.f, 0.f}, kq[2] = {0.f, 0.f};
 #pragma unroll
-      for (int ii = 0; ii < DPT; ++ii) {
-        const int i = ii * rl + r;
-        S[ii] *= GATED ? gt[i] : dec;
-        if (DELTA) dot[ii & 3] = fmaf(S[ii], kt[i], dot[ii & 3]);
+        for (int v = 0; v < DPT / 4; ++v) {
+          kk[v] = kt[v];
+          const float4 qq = qt[v];
+          if (GATED) {
+            const float4 g = gt[v];
+            S[4 * v] *= g.x; S[4 * v + 1] *= g.y; S[4 * v + 2] *= g.z; S[4 * v + 3] *= g.w;
+          } else {
+            S[4 * v] *= dec; S[4 * v + 1] *= dec; S[4 * v + 2] *= dec; S[4 * v + 3] *= dec;
+          }
+          dot[0] = fmaf(S[4 * v], kk[v].x, dot[0]);
+          dot[1] = fmaf(S[4 * v + 1], kk[v].y, dot[1]);
+          dot[0] = fmaf(S[4 * v + 2], kk[v].z, dot[0]);
+          dot[1] = fmaf(S[4 * v + 3], kk[v].w, dot[1]);
+          oq[0] = fmaf(S[4 * v], qq.x, oq[0]);
+          oq[1] = fmaf(S[4 * v + 1], qq.y, oq[1]);
+          oq[0] = fmaf(S[4 * v + 2], qq.z, oq[0]);
+          oq[1] = fmaf(S[4 * v + 3], qq.w, oq[1]);
+          kq[0] = fmaf(kk[v].x, qq.x, kq[0]);
+          kq[1] = fmaf(kk[v].y, qq.y, kq[1]);
+          kq[0] = fmaf(kk[v].z, qq.z, kq[0]);
+          kq[1] = fmaf(kk[v].w, qq.w, kq[1]);
+        }
+        float sum = dot[0] + dot[1], sq_ = oq[0] + oq[1], skq = kq[0] + kq[1];
+#pragma unroll
+        for (int o = cols_per_warp; o < 32; o <<= 1) {
+          sum += __shfl_xor_sync(0xffffffffu, sum, o);
+          sq_ += __shfl_xor_sync(0xffffffffu, sq_, o);
+          skq += __shfl_xor_sync(0xffffffffu, skq, o);
+        }
+        const float u = bs[tt] * (vs[tt * cols + col_local] - sum);
+        o_sum = fmaf(u, skq, sq_);
+#pragma unroll
+        for (int v = 0; v < DPT / 4; ++v) {
+          S[4 * v] = fmaf(kk[v].x, u, S[4 * v]);
+          S[4 * v + 1] = fmaf(kk[v].y, u, S[4 * v + 1]);
+          S[4 * v + 2] = fmaf(kk[v].z, u, S[4 * v + 2]);
+          S[4 * v + 3] = fmaf(kk[v].w, u, S[4 * v + 3]);
+        }
+      } else {
+        const float u = vs[tt * cols + col_local];
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int v = 0; v < DPT / 4; ++v) {
+          kk[v] = kt[v];
+          const float4 qq = qt[v];
+          if (GATED) {
+            const float4 g = gt[v];
+            S[4 * v] *= g.x; S[4 * v + 1] *= g.y; S[4 * v + 2] *= g.z; S[4 * v + 3] *= g.w;
+          } else {
+            S[4 * v] *= dec; S[4 * v + 1] *= dec; S[4 * v + 2] *= dec; S[4 * v + 3] *= dec;
+          }
+          S[4 * v] = fmaf(kk[v].x, u, S[4 * v]);
+          S[4 * v + 1] = fmaf(kk[v].y, u, S[4 * v + 1]);
+          S[4 * v + 2] = fmaf(kk[v].z, u, S[4 * v + 2]);
+          S[4 * v + 3] = fmaf(kk[v].w, u, S[4 * v + 3]);
+          acc[0] = fmaf(S[4 * v], qq.x, acc[0]);
+          acc[1] = fmaf(S[4 * v + 1], qq.y, acc[1]);
+          acc[2] = fmaf(S[4 * v + 2], qq.z, acc[2]);
+          acc[3] = fmaf(S[4 * v + 3], qq.w, acc[3]);
+        }
+        o_sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+#pragma unroll
+        for (int o = cols_per_warp; o < 32; o <<= 1) o_sum += __shfl_xor_sync(0xffffffffu, o_sum, o);
       }
-      float u = vs[tt * cols + col_local];
-      if (DELTA) {
-        float sum = (dot[0] + dot[1]) + (dot[2] + dot[3]);
-#pragma unroll
-        for (int o = cols_per_warp; o < 32; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-        u = bs[tt] * (u - sum);
-      }
-      float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int ii = 0; ii < DPT; ++ii) {
-        const int i = ii * rl + r;
-        S[ii] = fmaf(kt[i], u, S[ii]);
-        acc[ii & 3] = fmaf(S[ii], qt[i], acc[ii & 3]);
-      }
-      float o_sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-#pragma unroll
-      for (int o = cols_per_warp; o < 32; o <<= 1) o_sum += __shfl_xor_sync(0xffffffffu, o_sum, o);
       if (live && r == 0) p.out[static_cast<size_t>(t0 + tt) * p.ldo + h * dv + col] = o_sum;
     }
   }
 #pragma unroll
   for (int ii = 0; ii < DPT; ++ii) {
-    const int i = ii * rl + r;
+    const int i = r * DPT + ii;
     if (live && i < d) sbase[static_cast<size_t>(i) * dv + col] = S[ii];
   }
 }

@@ -3,7 +3,7 @@
 A pre-norm decoder whose layers carry one of two mixers: ``parallel`` (softmax attention with a sink,
 a soft cap, a bias by distance and a query temperature, beside linear attention with a constant decay
 per head; the mean of their normalised outputs) or ``channel_delta`` (the delta rule with a decay per
-key channel behind short convolutions).  Norm weights are stored around zero (``1 + w``); the
+key channel behind short convolutions).  Norm weights are kept as offsets from one (``1 + w``); the
 feed-forward is a gated unit with limits and biases; the output head is the embedding table.  A run of
 layers may be passed several times with the same weights: every pass has caches and states of its own,
 and starts by adding the embedding's output (not in the first pass) and a row of ``loop.step``.

@@ -15,7 +15,7 @@ from .base import NORMS, Norm, Runtime
 class RMSNorm(Norm):
     """``y = w * x * rsqrt(mean(x^2) + eps)``: statistics in float32, the weight
     applied as ``w`` (mini_llm/nn/norm.py:42-46).  Random weights are
-    ``1 + N(0, 0.05)``.  With ``offset`` the stored weight lies around zero and the
+    ``1 + N(0, 0.05)``.  With ``offset`` the stored weight is the distance from that offset and the
     factor is ``offset + w`` (formed once, in float32, when the weight is placed);
     random weights are then ``N(0, 0.05)``."""
 

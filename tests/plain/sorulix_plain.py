@@ -39,7 +39,7 @@ def rms(x: torch.Tensor, eps: float) -> torch.Tensor:
 
 
 def norm_around_zero(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
-    """The layer norms store their weight around zero: ``rms(x) * (1 + w)``."""
+    """The layer norms keep their weight as an offset from one: ``rms(x) * (1 + w)``."""
 
     return rms(x, eps) * (1.0 + w)
 

@@ -1,5 +1,6 @@
 from .fields import read_config_dict, required, optional
 from .qwen3 import Qwen3Config
+from .ropulix import RopulixConfig
 from .sorulix import SorulixConfig
 from .registry import (
     Architecture,
@@ -12,6 +13,7 @@ from .registry import (
 __all__ = [
     "Architecture",
     "Qwen3Config",
+    "RopulixConfig",
     "SorulixConfig",
     "architecture_for",
     "load_config",

@@ -17,16 +17,15 @@
 
 namespace b200 {
 
-constexpr int kMaxChunks = 8;  // head_dim <= 256
-
-template <typename T>
+// kMaxChunks x 32 columns of values at most; the key size is bounded by shared memory only
+template <typename T, int kMaxChunks>
 __global__ void __launch_bounds__(128)
 paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_pool,
                             const T* __restrict__ v_pool, T* __restrict__ out,
                             const int* __restrict__ positions, const int* __restrict__ token_entry,
                             const int* __restrict__ block_table, int table_stride, int page_size,
                             int nq, int nkv, int d, float scale, int window, int dv, float softcap,
-                            const float* __restrict__ slopes, int sink) {
+                            const float* __restrict__ slopes, int sink, int v_row) {
   extern __shared__ float smem[];
   pdl_trigger();
   pdl_wait();
@@ -89,7 +88,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_poo
       if (pj == 0.f) continue;
       const int tj = t0 + j;
       const int page = table[tj / page_size];
-      const T* vrow = v_pool + ((static_cast<size_t>(page) * nkv + kvh) * page_size + tj % page_size) * dv;
+      const T* vrow = v_pool + ((static_cast<size_t>(page) * nkv + kvh) * page_size + tj % page_size) * v_row;
 #pragma unroll
       for (int c = 0; c < kMaxChunks; ++c) {
         const int i = lane + 32 * c;
@@ -109,27 +108,44 @@ paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_poo
 
 }  // namespace b200
 
-// q [n, nq, d], keys [pages, nkv, page_size, d], values [pages, nkv, page_size, dv], out [n, nq, dv].
-// softcap <= 0: no cap; slopes (nq floats) may be null; sink 0 or 1.
+// q [n, nq, d], keys [pages, nkv, page_size, d], values [pages, nkv, page_size, v_row] of which the first dv columns are read
+// (v_row = dv: a pool of its own; v_row = d with v_pool = k_pool: the values are the leading columns of the keys),
+// out [n, nq, dv].  softcap <= 0: no cap; slopes (nq floats) may be null; sink 0 or 1.
+extern "C" int b200_paged_attention_simt_strided(
+    const void* q, const void* k_pool, const void* v_pool, void* out, const int* positions,
+    const int* token_entry, const int* block_table, int table_stride, int page_size, int n,
+    int nq, int nkv, int d, int dv, int v_row, float scale, int window, float softcap, const float* slopes, int sink,
+    int dtype, cudaStream_t stream) {
+  using namespace b200;
+  if (n <= 0) return 0;
+  if (d <= 0 || dv <= 0 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || v_row < dv)
+    return B200_ERR_BAD_SIZE;
+  if (dv > 32 * 20 || d > 2048) return B200_ERR_TOO_LARGE;
+  dim3 grid(n, (nq + 3) / 4);
+  if (grid.y > 65535) return B200_ERR_TOO_LARGE;
+  const size_t smem = static_cast<size_t>(4) * d * sizeof(float);
+#define B200_SIMT_ATTENTION(CH)                                                                             \
+  B200_DISPATCH_DTYPE(dtype, T,                                                                             \
+      launch(paged_attention_simt_kernel<T, CH>, dim3(grid), dim3(128), smem, stream,                       \
+          static_cast<const T*>(q), static_cast<const T*>(k_pool), static_cast<const T*>(v_pool),          \
+          static_cast<T*>(out), positions, token_entry, block_table, table_stride, page_size, nq,           \
+          nkv, d, scale, window, dv, softcap, slopes, sink, v_row))
+  if (dv <= 64) { B200_SIMT_ATTENTION(2); }
+  else if (dv <= 128) { B200_SIMT_ATTENTION(4); }
+  else if (dv <= 256) { B200_SIMT_ATTENTION(8); }
+  else { B200_SIMT_ATTENTION(20); }
+#undef B200_SIMT_ATTENTION
+  return launch_status();
+}
+
 extern "C" int b200_paged_attention_simt_rules(
     const void* q, const void* k_pool, const void* v_pool, void* out, const int* positions,
     const int* token_entry, const int* block_table, int table_stride, int page_size, int n,
     int nq, int nkv, int d, int dv, float scale, int window, float softcap, const float* slopes, int sink,
     int dtype, cudaStream_t stream) {
-  using namespace b200;
-  if (n <= 0) return 0;
-  if (d <= 0 || dv <= 0 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0)
-    return B200_ERR_BAD_SIZE;
-  if (d > 32 * kMaxChunks || dv > 32 * kMaxChunks) return B200_ERR_TOO_LARGE;
-  dim3 grid(n, (nq + 3) / 4);
-  if (grid.y > 65535) return B200_ERR_TOO_LARGE;
-  const size_t smem = static_cast<size_t>(4) * d * sizeof(float);
-  B200_DISPATCH_DTYPE(dtype, T,
-      launch(paged_attention_simt_kernel<T>, dim3(grid), dim3(128), smem, stream, 
-          static_cast<const T*>(q), static_cast<const T*>(k_pool), static_cast<const T*>(v_pool),
-          static_cast<T*>(out), positions, token_entry, block_table, table_stride, page_size, nq,
-          nkv, d, scale, window, dv, softcap, slopes, sink));
-  return launch_status();
+  if (d > 256 || dv > 256) return B200_ERR_TOO_LARGE;
+  return b200_paged_attention_simt_strided(q, k_pool, v_pool, out, positions, token_entry, block_table, table_stride, page_size,
+                                           n, nq, nkv, d, dv, dv, scale, window, softcap, slopes, sink, dtype, stream);
 }
 
 extern "C" int b200_paged_attention_simt(

@@ -1,0 +1,276 @@
+// Matrix products in groups: one weight per batch index (heads, diagonal blocks), or one weight per group of rows
+// that a router has sent to the same expert.  C = A * W^T (+ bias), float accumulation in ascending k inside one
+// thread, so a row's result depends neither on the other rows of the batch nor on where the row sits in its tile.
+// Storage types float32 (FFMA only: the verification path) and bfloat16 (CUDA cores; the tensor-core form of the
+// same tiles lives in gemm_grouped_mma.cu).  Also the router of a mixture of experts and the bookkeeping that sorts
+// (token, choice) pairs by expert without the host knowing the counts.
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int BM = 64, BN = 64, BK = 16;
+
+struct GroupedArgs {
+  const void* A; long long lda, a_z;        // rows of A; a_z: elements between batch entries
+  const int* row_index;                     // per row of the tile space: source row or validity (< 0: the row is padding)
+  int gather;                               // 1: row_index names the row of A; 0: row m of A is used, row_index only says valid
+  const void* W; long long ldw, w_z;        // W[z]: [N, K] with row stride ldw, or (k_major) [K, N]
+  int k_major;
+  const float* bias; long long bias_z;
+  void* C; long long ldc, c_z;
+  const int* tile_group;                    // per row tile: the group (expert) whose weight it uses, < 0: nothing to do
+  int M, N, K;
+};
+
+template <typename TIn, typename TOut, int ACT>
+__global__ void __launch_bounds__(256)
+grouped_gemm_kernel(const GroupedArgs g) {
+  __shared__ float As[BK][BM + 4];
+  __shared__ float Ws[BK][BN + 4];
+  __shared__ int src_row[BM];
+  pdl_trigger();
+  pdl_wait();
+  const int tid = threadIdx.x;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  int z = blockIdx.z;
+  long long a_off = z * g.a_z, c_off = z * g.c_z;
+  if (g.tile_group != nullptr) {
+    z = g.tile_group[blockIdx.y];
+    if (z < 0) return;
+    a_off = c_off = 0;
+  }
+  const TIn* A = static_cast<const TIn*>(g.A) + a_off;
+  const TIn* W = static_cast<const TIn*>(g.W) + z * g.w_z;
+  const float* bias = g.bias ? g.bias + z * g.bias_z : nullptr;
+  TOut* C = static_cast<TOut*>(g.C) + c_off;
+  if (tid < BM) {
+    const int m = m0 + tid;
+    int r = m < g.M ? m : -1;
+    if (r >= 0 && g.row_index != nullptr) {
+      const int v = g.row_index[m];
+      r = v < 0 ? -1 : (g.gather ? v : m);
+    }
+    src_row[tid] = r;
+  }
+  __syncthreads();
+  const int tx = tid & 15, ty = tid >> 4;
+  float acc[4][4] = {};
+  const int lrow = tid >> 2, lk = (tid & 3) * 4;
+  const int arow = src_row[lrow];
+  const int wn = n0 + lrow;
+  for (int k0 = 0; k0 < g.K; k0 += BK) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int k = k0 + lk + i;
+      As[lk + i][lrow] = (arow >= 0 && k < g.K) ? to_float(A[arow * g.lda + k]) : 0.f;
+      float w = 0.f;
+      if (wn < g.N && k < g.K) w = to_float(g.k_major ? W[k * g.ldw + wn] : W[wn * g.ldw + k]);
+      Ws[lk + i][lrow] = w;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < BK; ++k) {
+      float a[4], w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[k][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) w[j] = Ws[k][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty * 4 + i;
+    if (src_row[ty * 4 + i] < 0) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n >= g.N) continue;
+      float v = acc[i][j] + (bias ? bias[n] : 0.f);
+      if (ACT == 1) {          // the square of relu
+        v = fmaxf(v, 0.f);
+        v *= v;
+      }
+      C[m * g.ldc + n] = from_float<TOut>(v);
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------- router
+// One warp per token: logits z = W_r h + b in float32 (W_r float32 [experts, width], h in the activation type), the `top`
+// largest (the lower index wins a tie), weights = softmax over the chosen logits only.
+template <typename T>
+__global__ void __launch_bounds__(128)
+route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ br, int* __restrict__ ids,
+             float* __restrict__ wts, int n, int width, int experts, int top) {
+  extern __shared__ float logits_all[];
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int token = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (token >= n) return;
+  float* logits = logits_all + warp * experts;
+  const T* row = h + static_cast<size_t>(token) * width;
+  for (int e = 0; e < experts; ++e) {
+    const float* w = wr + static_cast<size_t>(e) * width;
+    float dot = 0.f;
+    for (int i = lane; i < width; i += 32) dot = fmaf(to_float(row[i]), w[i], dot);
+    dot = warp_sum(dot);
+    if (lane == 0) logits[e] = dot + (br ? br[e] : 0.f);
+  }
+  __syncwarp();
+  float first = 0.f, total = 0.f, mine = 0.f;
+  int my_id = 0;
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32) {
+      const float v = logits[e];
+      if (v > best) { best = v; at = e; }       // ascending e: the first of equals stays
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+    }
+    if (j == 0) first = best;
+    const float p = expf(best - first);
+    total += p;
+    if (lane == j) { mine = p; my_id = at; }
+    __syncwarp();
+    if (lane == 0) logits[at] = -INFINITY;
+    __syncwarp();
+  }
+  if (lane < top) {
+    ids[static_cast<size_t>(token) * top + lane] = my_id;
+    wts[static_cast<size_t>(token) * top + lane] = mine / total;
+  }
+}
+
+// One CTA.  Counts the pairs of every expert, lays the experts' rows out one behind the other, each padded to whole
+// tiles of BM rows, and gives every pair its row: sorted_token[row] = token (-1 in the padding), pair_row[pair] = row,
+// tile_group[tile] = expert (-1 behind the last used tile).
+__global__ void __launch_bounds__(1024)
+plan_kernel(const int* __restrict__ ids, int pairs, int top, int experts, int* __restrict__ sorted_token, int* __restrict__ pair_row,
+            int* __restrict__ tile_group, int max_tiles) {
+  extern __shared__ int sh[];
+  int* count = sh;                 // [experts]
+  int* start = sh + experts;       // [experts + 1], in rows
+  pdl_trigger();
+  pdl_wait();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
+  for (int r = threadIdx.x; r < max_tiles * BM; r += blockDim.x) sorted_token[r] = -1;
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&count[ids[p]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0;
+    for (int e = 0; e < experts; ++e) {
+      start[e] = at;
+      at += (count[e] + BM - 1) / BM * BM;
+      count[e] = 0;
+    }
+    start[experts] = at;
+  }
+  __syncthreads();
+  for (int t = threadIdx.x; t < max_tiles; t += blockDim.x) {
+    const int row = t * BM;
+    int group = -1;
+    if (row < start[experts]) {
+      int lo = 0, hi = experts - 1;          // the last expert whose start is <= row and that has rows
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (start[mid] <= row) lo = mid; else hi = mid - 1;
+      }
+      group = lo;
+    }
+    tile_group[t] = group;
+  }
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+    const int e = ids[p];
+    const int row = start[e] + atomicAdd(&count[e], 1);
+    sorted_token[row] = p / top;
+    pair_row[p] = row;
+  }
+}
+
+// out[t] = sum_j wts[t, j] * rows[pair_row[t, j]], j ascending.
+__global__ void __launch_bounds__(256)
+combine_kernel(const float* __restrict__ rows, const int* __restrict__ pair_row, const float* __restrict__ wts, float* __restrict__ out,
+               int width, int top) {
+  pdl_trigger();
+  pdl_wait();
+  const int token = blockIdx.x;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < top; ++j) {
+      const int p = token * top + j;
+      acc = fmaf(wts[p], rows[static_cast<size_t>(pair_row[p]) * width + c], acc);
+    }
+    out[static_cast<size_t>(token) * width + c] = acc;
+  }
+}
+
+template <typename TIn, typename TOut>
+int launch_grouped(const GroupedArgs& g, int batch, int act, cudaStream_t stream) {
+  dim3 grid((g.N + BN - 1) / BN, (g.M + BM - 1) / BM, batch);
+  if (grid.y > 65535 || grid.z > 65535) return B200_ERR_TOO_LARGE;
+  if (act == 1) launch(grouped_gemm_kernel<TIn, TOut, 1>, grid, dim3(256), 0, stream, g);
+  else launch(grouped_gemm_kernel<TIn, TOut, 0>, grid, dim3(256), 0, stream, g);
+  return launch_status();
+}
+
+}  // namespace b200
+
+// in_dtype: storage type of A and W; out_dtype: of C.  batch > 1 walks a_z / w_z / bias_z / c_z; with tile_group the
+// weight of a row tile is W + tile_group[tile] * w_z instead (batch must be 1).  act: 0 none, 1 relu squared.
+extern "C" int b200_gemm_grouped(const void* A, long long lda, long long a_z, const int* row_index, int gather, const void* W,
+                                 long long ldw, long long w_z, int k_major, const float* bias, long long bias_z, void* C,
+                                 long long ldc, long long c_z, const int* tile_group, int M, int N, int K, int batch, int act,
+                                 int in_dtype, int out_dtype, cudaStream_t stream) {
+  using namespace b200;
+  if (M <= 0 || N <= 0 || batch <= 0) return 0;
+  if (K <= 0 || (tile_group != nullptr && batch != 1)) return B200_ERR_BAD_SIZE;
+  GroupedArgs g{A, lda, a_z, row_index, gather, W, ldw, w_z, k_major, bias, bias_z, C, ldc, c_z, tile_group, M, N, K};
+  if (in_dtype == kF32 && out_dtype == kF32) return launch_grouped<float, float>(g, batch, act, stream);
+  if (in_dtype == kBF16 && out_dtype == kBF16) return launch_grouped<__nv_bfloat16, __nv_bfloat16>(g, batch, act, stream);
+  if (in_dtype == kBF16 && out_dtype == kF32) return launch_grouped<__nv_bfloat16, float>(g, batch, act, stream);
+  return B200_ERR_BAD_DTYPE;
+}
+
+extern "C" int b200_moe_route(const void* h, const float* wr, const float* br, int* ids, float* wts, int n, int width, int experts,
+                              int top, int dtype, cudaStream_t stream) {
+  using namespace b200;
+  if (n <= 0) return 0;
+  if (width <= 0 || experts <= 0 || top <= 0 || top > experts || top > 32 || experts > 2048) return B200_ERR_BAD_SIZE;
+  const size_t smem = sizeof(float) * 4 * experts;
+  B200_DISPATCH_DTYPE(dtype, T, launch(route_kernel<T>, dim3((n + 3) / 4), dim3(128), smem, stream, static_cast<const T*>(h), wr, br,
+                                       ids, wts, n, width, experts, top));
+  return launch_status();
+}
+
+extern "C" int b200_moe_tile_rows() { return b200::BM; }
+
+extern "C" int b200_moe_plan(const int* ids, int pairs, int top, int experts, int* sorted_token, int* pair_row, int* tile_group,
+                             int max_tiles, cudaStream_t stream) {
+  using namespace b200;
+  if (pairs <= 0) return 0;
+  if (experts <= 0 || experts > 2048 || top <= 0 || max_tiles * BM < pairs) return B200_ERR_BAD_SIZE;
+  launch(plan_kernel, dim3(1), dim3(1024), sizeof(int) * (2 * experts + 1), stream, ids, pairs, top, experts, sorted_token, pair_row,
+         tile_group, max_tiles);
+  return launch_status();
+}
+
+extern "C" int b200_moe_combine(const float* rows, const int* pair_row, const float* wts, float* out, int n, int width, int top,
+                                cudaStream_t stream) {
+  using namespace b200;
+  if (n <= 0) return 0;
+  if (width <= 0 || top <= 0) return B200_ERR_BAD_SIZE;
+  launch(combine_kernel, dim3(n), dim3(256), 0, stream, rows, pair_row, wts, out, width, top);
+  return launch_status();
+}

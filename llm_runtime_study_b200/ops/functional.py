@@ -278,3 +278,27 @@ def add_rows(resid: torch.Tensor, a: torch.Tensor | None = None, b: torch.Tensor
     if vector is not None:
         require(vector, "vector", dtype=torch.float32, shape=(hidden,))
     call("b200_add_rows", ptr(resid), ptr(a), ptr(b), ptr(vector), n, hidden, stream_ptr())
+
+
+def paged_attention_simt_latent(
+    q: torch.Tensor, pool: torch.Tensor, *, value_dim: int, positions: torch.Tensor, token_entry: torch.Tensor,
+    block_table: torch.Tensor, scale: float, window: int = 0,
+) -> torch.Tensor:
+    """Causal attention of every query head over one shared row per token whose leading ``value_dim`` columns are also the
+    value: q ``[N, heads, d]``, pool ``[pages, page_size, d]``, result ``[N, heads, value_dim]``.  32-bit arithmetic, tiles
+    of 32 keys from key 0 of the window's first tile, so the order of every sum depends on the token's position alone."""
+
+    require(q, "q", dims=3)
+    n, nq, d = q.shape
+    require(pool, "pool", dtype=q.dtype, dims=3)
+    page_size = pool.shape[1]
+    if pool.shape[2] != d or not 0 < value_dim <= d:
+        raise KernelError(f"q head size {d}, pool {tuple(pool.shape)} and value size {value_dim} do not fit")
+    require(positions, "positions", dtype=torch.int32, shape=(n,))
+    require(token_entry, "token_entry", dtype=torch.int32, shape=(n,))
+    require(block_table, "block_table", dtype=torch.int32, dims=2)
+    out = torch.empty((n, nq, value_dim), dtype=q.dtype, device=q.device)
+    call("b200_paged_attention_simt_strided", ptr(q), ptr(pool), ptr(pool), ptr(out), ptr(positions), ptr(token_entry),
+         ptr(block_table), block_table.shape[1], page_size, n, nq, 1, d, value_dim, d, float(scale), int(window), 0.0, None, 0,
+         tag(q.dtype), stream_ptr())
+    return out

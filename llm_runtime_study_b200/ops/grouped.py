@@ -1,0 +1,123 @@
+"""Matrix products in groups (one weight per head or diagonal block; one weight per expert for the rows a router sent
+there) and the router's kernels.  Nothing here asks the device how many rows an expert received: the launch is sized for
+the worst case and tiles without rows leave at once, so a step can be replayed from a CUDA graph."""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ..errors import KernelError
+from .native import call, ptr, query, require, stream_ptr, tag
+
+
+def batched_linear(
+    a: torch.Tensor, weight: torch.Tensor, *, batch: int, k: int, n_out: int, a_batch_stride: int, weight_k_major: bool = False,
+    bias: torch.Tensor | None = None, out: torch.Tensor | None = None, out_batch_stride: int | None = None,
+    out_dtype: torch.dtype | None = None,
+) -> torch.Tensor:
+    """For ``z`` in ``range(batch)``: ``out[:, z * out_batch_stride : + n_out] = a[:, z * a_batch_stride : + k] @ W[z]^T (+ bias[z])``.
+    ``weight`` is ``[batch, n_out, k]`` or, with ``weight_k_major``, ``[batch, k, n_out]`` (then ``W[z]^T`` is the stored matrix
+    itself).  ``a`` and ``out`` are rows ``[M, ...]`` with unit column stride; ``out`` may be given (a column block of a wider
+    tensor is fine).  float accumulation in ascending ``k``."""
+
+    require(a, "a", dims=2)
+    require(weight, "weight", dtype=a.dtype, dims=3)
+    m = a.shape[0]
+    expect = (batch, k, n_out) if weight_k_major else (batch, n_out, k)
+    if tuple(weight.shape) != expect:
+        raise KernelError(f"weight has shape {tuple(weight.shape)}, expected {expect}")
+    if (batch - 1) * a_batch_stride + k > a.shape[1]:
+        raise KernelError("batched_linear: a batch entry's columns lie outside a")
+    if bias is not None:
+        require(bias, "bias", dtype=torch.float32, shape=(batch, n_out))
+    out_dtype = out_dtype or a.dtype
+    if out is None:
+        out_batch_stride = n_out if out_batch_stride is None else out_batch_stride
+        out = torch.empty((m, batch * out_batch_stride), dtype=out_dtype, device=a.device)
+    else:
+        if out.dim() != 2 or out.shape[0] != m or out.stride(1) != 1 or out.device != a.device:
+            raise KernelError("batched_linear: out must be rows on the same device with unit column stride")
+        if out_batch_stride is None or (batch - 1) * out_batch_stride + n_out > out.shape[1]:
+            raise KernelError("batched_linear: a batch entry's results lie outside out")
+    call("b200_gemm_grouped", ptr(a), a.stride(0), a_batch_stride, None, 0, ptr(weight), weight.stride(1), weight.stride(0),
+         1 if weight_k_major else 0, ptr(bias), n_out, out.data_ptr(), out.stride(0), out_batch_stride, None, m, n_out, k, batch, 0,
+         tag(a.dtype), tag(out.dtype), stream_ptr())
+    return out
+
+
+@dataclass
+class Routing:
+    """Where a router sent the tokens.  ``ids``/``weights`` ``[N, top]``; ``pair_row[N * top]``: the row of each (token, choice)
+    pair in the expert-sorted order; ``sorted_token[rows]``: the token of a sorted row (-1: padding up to whole tiles);
+    ``tile_group[tiles]``: the expert of each tile of rows (-1: unused)."""
+
+    ids: torch.Tensor
+    weights: torch.Tensor
+    pair_row: torch.Tensor
+    sorted_token: torch.Tensor
+    tile_group: torch.Tensor
+    top: int
+
+    @property
+    def rows(self) -> int:
+        return self.sorted_token.shape[0]
+
+
+def tile_rows() -> int:
+    return query("b200_moe_tile_rows")
+
+
+def route(h: torch.Tensor, router: torch.Tensor, bias: torch.Tensor | None, *, top: int) -> Routing:
+    """Logits ``router @ h + bias`` in float32 (``router`` float32 ``[experts, width]``; ``h`` in the activation type), the ``top``
+    largest chosen (the lower index wins a tie), weights the softmax over the chosen logits; then the pairs sorted by expert,
+    each expert's rows padded to whole tiles."""
+
+    require(h, "h", dims=2)
+    n, width = h.shape
+    require(router, "router", dtype=torch.float32, dims=2)
+    experts = router.shape[0]
+    if router.shape[1] != width:
+        raise KernelError(f"router has shape {tuple(router.shape)}, expected [experts, {width}]")
+    if bias is not None:
+        require(bias, "bias", dtype=torch.float32, shape=(experts,))
+    dev = h.device
+    ids = torch.empty((n, top), dtype=torch.int32, device=dev)
+    weights = torch.empty((n, top), dtype=torch.float32, device=dev)
+    call("b200_moe_route", ptr(h), ptr(router), ptr(bias), ptr(ids), ptr(weights), n, width, experts, top, tag(h.dtype), stream_ptr())
+    tile = tile_rows()
+    max_tiles = min(-(-n * top // tile) + experts, n * top)       # a tile holds one expert's rows only
+    pair_row = torch.empty(n * top, dtype=torch.int32, device=dev)
+    sorted_token = torch.empty(max_tiles * tile, dtype=torch.int32, device=dev)
+    tile_group = torch.empty(max_tiles, dtype=torch.int32, device=dev)
+    call("b200_moe_plan", ptr(ids), n * top, top, experts, ptr(sorted_token), ptr(pair_row), ptr(tile_group), max_tiles, stream_ptr())
+    return Routing(ids, weights, pair_row, sorted_token, tile_group, top)
+
+
+def expert_linear(a: torch.Tensor, weight: torch.Tensor, routing: Routing, *, gather: bool, act: str | None = None,
+                  out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """``out[row] = act(W[expert of row] @ a[source of row])`` for every sorted row.  ``weight`` ``[experts, n_out, k]``.  With
+    ``gather`` the source is the row's token (``a`` is ``[N, k]``); otherwise ``a`` is already in sorted order (``[rows, k]``).
+    ``act``: ``"relu2"`` (the square of relu) or ``None``.  Rows of the padding are not written."""
+
+    require(a, "a", dims=2)
+    require(weight, "weight", dtype=a.dtype, dims=3)
+    experts, n_out, k = weight.shape
+    if a.shape[1] != k or (not gather and a.shape[0] != routing.rows):
+        raise KernelError(f"expert_linear: a {tuple(a.shape)} does not fit the weight {tuple(weight.shape)} and {routing.rows} sorted rows")
+    out = torch.empty((routing.rows, n_out), dtype=out_dtype or a.dtype, device=a.device)
+    call("b200_gemm_grouped", ptr(a), a.stride(0), 0, ptr(routing.sorted_token), 1 if gather else 0, ptr(weight), weight.stride(1),
+         weight.stride(0), 0, None, 0, ptr(out), out.stride(0), 0, ptr(routing.tile_group), routing.rows, n_out, k, 1,
+         {None: 0, "relu2": 1}[act], tag(a.dtype), tag(out.dtype), stream_ptr())
+    return out
+
+
+def combine(rows: torch.Tensor, routing: Routing) -> torch.Tensor:
+    """``out[t] = sum_j weights[t, j] * rows[pair_row[t, j]]`` (float32, ``j`` ascending)."""
+
+    require(rows, "rows", dtype=torch.float32, dims=2)
+    n = routing.ids.shape[0]
+    out = torch.empty((n, rows.shape[1]), dtype=torch.float32, device=rows.device)
+    call("b200_moe_combine", ptr(rows), ptr(routing.pair_row), ptr(routing.weights), ptr(out), n, rows.shape[1], routing.top, stream_ptr())
+    return out

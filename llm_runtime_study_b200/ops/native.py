@@ -18,7 +18,7 @@ import torch
 from ..csrc.build import load_library
 from ..errors import KernelError
 
-c_int, c_float, c_void_p = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
+c_int, c_float, c_void_p, c_longlong = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
 
 DTYPE_TAG = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -68,6 +68,10 @@ _LIBRARIES = {
                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                 c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_int, c_int, c_void_p,
             ],
+            "b200_paged_attention_simt_strided": [
+                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_int, c_int, c_void_p,
+            ],
         },
     ),
     "b200_sequence_state": (
@@ -85,6 +89,40 @@ _LIBRARIES = {
             "b200_conv_state_update": [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
             "b200_group_norm_gate": [c_void_p, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p,
                                      c_void_p, c_int, c_void_p],
+        },
+    ),
+    "b200_mixer_steps": (
+        ("mixer_steps.cu",),
+        {
+            "b200_head_norm_write": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_void_p,
+                                     c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+            "b200_latent_prepare": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
+                                    c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p],
+            "b200_rope_slice": [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                c_void_p, c_int, c_int, c_void_p],
+            "b200_sigmoid_gate": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+            "b200_norm_accumulate_round": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
+        },
+    ),
+    "b200_rglru": (
+        ("rglru.cu",),
+        {
+            "b200_conv_taps": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                               c_int, c_int, c_int, c_void_p],
+            "b200_gated_recurrence": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
+                                      c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        },
+    ),
+    "b200_gemm_grouped": (
+        ("gemm_grouped.cu",),
+        {
+            "b200_gemm_grouped": [c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_void_p, c_longlong, c_longlong, c_int,
+                                  c_void_p, c_longlong, c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_int, c_int, c_int,
+                                  c_int, c_int, c_int, c_void_p],
+            "b200_moe_route": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+            "b200_moe_tile_rows": [],
+            "b200_moe_plan": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+            "b200_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         },
     ),
 }

@@ -238,6 +238,7 @@ class ResidualStream:
     delta: torch.Tensor | None = None
     weighted: WeightedRows | None = None
     weighted_for: Any = None
+    rounded: torch.Tensor | None = None     # the residual rows in the activation type, where the last block made that copy
 
     def take_rows(self, norm: "Norm", consumer: Any) -> "torch.Tensor | WeightedRows":
         """What ``consumer`` gets as the rows normalised by ``norm``."""
@@ -252,7 +253,7 @@ class ResidualStream:
         """Record what a part returned: its output (to be added by the next norm), ``None`` (it added its
         output itself), or the rows it prepared for ``norm`` (added, and that norm half done)."""
 
-        self.delta = self.weighted = self.weighted_for = None
+        self.delta = self.weighted = self.weighted_for = self.rounded = None
         if isinstance(out, WeightedRows):
             self.weighted, self.weighted_for = out, norm
         else:

@@ -81,3 +81,59 @@ class PreNormBlock(Block):
         if part.fuses_norms:
             return part.forward(*args, residual=resid, next_norm=next_norm)
         return part.forward(*args, residual=resid)
+
+
+@BLOCKS.register("output_norm")
+class OutputNormBlock(Block):
+    """``h = h + norm_1(mixer(h)); h = h + norm_2(ffn(h))``: the sublayers read the residual rows themselves (rounded to
+    the activation type where that is not float32) and the norm sits on their output only.  The kernel that normalises a
+    sublayer's output adds it into the float32 rows and hands the next sublayer its rounded copy in the same pass.
+    ``names`` as for ``pre_norm``; a layer without a feed-forward is its first half only."""
+
+    graph_safe = True
+
+    def __init__(
+        self, *, mixer: Mapping[str, Any], feed_forward: Mapping[str, Any] | None, mixer_norm: Mapping[str, Any],
+        ffn_norm: Mapping[str, Any] | None = None, names: Mapping[str, str] | None = None,
+    ) -> None:
+        self.names = {**_DEFAULT_NAMES, **(names or {})}
+        self.mixer = MIXERS.build(mixer)
+        self.mixer_norm = NORMS.build(mixer_norm)
+        self.feed_forward = FEED_FORWARDS.build(feed_forward) if feed_forward else None
+        self.ffn_norm = NORMS.build(ffn_norm) if feed_forward else None
+        if feed_forward and not ffn_norm:
+            raise ValueError("an output_norm block with a feed-forward needs the norm behind it (ffn_norm)")
+        for norm in (self.mixer_norm, self.ffn_norm):
+            if norm is not None and norm.fusable() is None:
+                raise ValueError("an output_norm block normalises with a norm of the form w * x * rsqrt(mean(x^2) + eps)")
+
+    def children(self):
+        return tuple(part for _, part in self._parts())
+
+    _parts = PreNormBlock._parts
+    tensor_specs = PreNormBlock.tensor_specs
+    load = PreNormBlock.load
+
+    def forward(self, stream: ResidualStream, ctx: Any, cache: Any) -> None:
+        from ..ops import mixer_steps as M
+
+        resid = stream.resid
+        if stream.delta is not None:
+            resid += stream.delta
+            stream.put(None, None)
+        act = self.runtime.dtype
+        rounds = act != torch.float32
+        # what the block before this one left for its reader, if it was a block of this kind
+        x = stream.rounded
+        stream.put(None, None)
+        if x is None:
+            x = M.norm_accumulate_round(None, None, 0.0, resid, act) if rounds else resid
+        out = self.mixer.forward(x, ctx, cache)
+        weight, eps = self.mixer_norm.fusable()
+        x = M.norm_accumulate_round(out, weight, eps, resid, act if rounds else None)
+        if self.feed_forward is not None:
+            out = self.feed_forward.forward(x if rounds else resid, ctx)
+            weight, eps = self.ffn_norm.fusable()
+            x = M.norm_accumulate_round(out, weight, eps, resid, act if rounds else None)
+        if rounds:
+            stream.rounded = x

@@ -269,3 +269,64 @@ def make_sorulix_dir(path: Path, config: dict, ranks: dict, seed: int, *, torch_
     (path / "config.json").write_text(json.dumps(config, indent=1), encoding="utf-8")
     write_file(path / "model.safetensors", state)
     return path, state
+
+
+# ----------------------------------------------------------------- Ropulix
+# Two small configurations that differ in every size and option.  A: a latent attention layer whose rows a later layer
+# borrows with a wider window, grouped heads sharing one key/value head, key and value sizes that differ and are no
+# multiples of 16, a layer without a feed-forward, experts of which one, two or all are used.  B: a recurrence without a
+# convolution and with one block, attention with as many key/value heads as query heads, latent attention without a
+# window and with a query rank that is no multiple of eight, a period-2 convolution.
+ROPULIX_A = {
+    "architecture": "Ropulix", "vocab": 211, "width": 64, "norm": {"eps": 1e-5},
+    "layers": [
+        {"type": "latent_attention", "mixer": {"heads": 3, "dim": 16, "rot_dim": 8, "vdim": 24, "kv_rank": 40, "q_rank": 48,
+                                               "mask": {"size": 9}, "rot": {"base": 1000.0, "dims": 8}, "scale": 0.35},
+         "mlp": {"kind": "moe", "expert": {"ff": 40}, "router": {"experts": 5, "top": 2}}},
+        {"type": "attention", "mixer": {"heads": 4, "kv_heads": 1, "dim": 16, "vdim": 16, "mask": {"size": 5}, "scale": 0.3}, "mlp": None},
+        {"type": "rglru", "mixer": {"width": 96, "blocks": 3, "conv": 4},
+         "mlp": {"kind": "moe", "expert": {"ff": 24}, "router": {"experts": 3, "top": 3}}},
+        {"type": "latent_attention", "mixer": {"heads": 2, "dim": 8, "rot_dim": 8, "vdim": 8, "kv_rank": 40, "q_rank": 16, "kv_from": 0,
+                                               "mask": {"size": 13}, "rot": {"base": 1000.0, "dims": 8}, "scale": 0.5},
+         "mlp": {"kind": "moe", "expert": {"ff": 32}, "router": {"experts": 4, "top": 1}}},
+        {"type": "attention", "mixer": {"heads": 2, "kv_heads": 2, "dim": 24, "vdim": 8, "scale": 0.2},
+         "mlp": {"kind": "moe", "expert": {"ff": 40}, "router": {"experts": 5, "top": 2}}},
+    ],
+}
+ROPULIX_B = {
+    "architecture": "Ropulix", "vocab": 131, "width": 48, "norm": {"eps": 1e-6},
+    "layers": [
+        {"type": "rglru", "mixer": {"width": 48, "blocks": 1, "conv": 1},
+         "mlp": {"kind": "moe", "expert": {"ff": 56}, "router": {"experts": 2, "top": 1}}},
+        {"type": "attention", "mixer": {"heads": 3, "kv_heads": 3, "dim": 32, "vdim": 32, "mask": {"size": 33}, "scale": 0.18},
+         "mlp": {"kind": "moe", "expert": {"ff": 16}, "router": {"experts": 6, "top": 3}}},
+        {"type": "latent_attention", "mixer": {"heads": 1, "dim": 24, "rot_dim": 16, "vdim": 40, "kv_rank": 24, "q_rank": 12,
+                                               "rot": {"base": 10000.0, "dims": 16}, "scale": 0.16}, "mlp": None},
+        {"type": "rglru", "mixer": {"width": 80, "blocks": 5, "conv": 2},
+         "mlp": {"kind": "moe", "expert": {"ff": 16}, "router": {"experts": 6, "top": 3}}},
+    ],
+}
+ROPULIX = {"A": (ROPULIX_A, 21, 4), "B": (ROPULIX_B, 22, 16)}   # config, seed, page size
+
+
+def make_ropulix_dir(path: Path, config: dict, seed: int, *, torch_dtype: str = "float32", gain: float = 6.0):
+    """Write a Ropulix model folder with random weights; return (path, {name: CPU tensor as stored}).  The matrices are
+    drawn ``gain`` times larger than the framework's default, so that gates, decays and routers are not all alike."""
+
+    from llm_runtime_study_b200.config import RopulixConfig
+    from llm_runtime_study_b200.models.description import tensor_schema
+    from llm_runtime_study_b200.models.ropulix import describe_ropulix
+    from llm_runtime_study_b200.weights.random_init import random_state
+    from llm_runtime_study_b200.weights.safetensors_io import write_file
+
+    schema = tensor_schema(describe_ropulix(RopulixConfig.from_dict(config)))
+    dtype = {"float32": torch.float32, "bfloat16": torch.bfloat16}[torch_dtype]
+    state = random_state(schema, seed, dtype=torch.float32, include_optional=False)
+    for name, tensor in state.items():
+        if tensor.dim() == 2 and not name.endswith((".conv", ".ra.b", ".ri.b", ".router")):
+            tensor *= gain
+    state = {name: tensor.to(dtype) for name, tensor in state.items()}
+    path.mkdir(parents=True, exist_ok=True)
+    (path / "config.json").write_text(json.dumps(config, indent=1), encoding="utf-8")
+    write_file(path / "model.safetensors", state)
+    return path, state

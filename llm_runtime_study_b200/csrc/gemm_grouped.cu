@@ -1,10 +1,12 @@
 // Matrix products in groups: one weight per batch index (heads, diagonal blocks), or one weight per group of rows
 // that a router has sent to the same expert.  C = A * W^T (+ bias), float accumulation in ascending k inside one
 // thread, so a row's result depends neither on the other rows of the batch nor on where the row sits in its tile.
-// Storage types float32 (FFMA only: the verification path) and bfloat16 (CUDA cores; the tensor-core form of the
-// same tiles lives in gemm_grouped_mma.cu).  Also the router of a mixture of experts and the bookkeeping that sorts
+// Storage types float32 (FFMA only: the verification path) and bfloat16: on the tensor cores (mma.sync m16n8k16, tiles
+// staged by cp.async in three stages) where rows and strides are multiples of 16 bytes, on CUDA cores otherwise.
+// Also the router of a mixture of experts and the bookkeeping that sorts
 // (token, choice) pairs by expert without the host knowing the counts.
 #include "common.cuh"
+#include "mma.cuh"
 
 namespace b200 {
 
@@ -98,6 +100,131 @@ grouped_gemm_kernel(const GroupedArgs g) {
       C[m * g.ldc + n] = from_float<TOut>(v);
     }
   }
+}
+
+// ----------------------------------------------------------------------------- bfloat16 on the tensor cores
+// The same tile space (BM rows of one group or batch entry) with BN = 128 columns and BK = 32 per stage.  Eight warps,
+// two along the rows and four along the columns, each 32 x 32 outputs.  Every 16-byte chunk of A and W must start on a
+// 16-byte boundary: base pointers, row strides and batch strides are multiples of 8 elements (the launcher checks).
+constexpr int TBN = 128, TBK = 32, TPAD = 8, TSTAGES = 3;
+constexpr int TLD = TBK + TPAD;                         // 40 halves = 80 bytes a row: ldmatrix reads hit every bank once
+constexpr int TSTAGE_HALVES = (BM + TBN) * TLD;
+
+template <typename TOut, int ACT>
+__global__ void __launch_bounds__(256)
+grouped_gemm_mma_kernel(const GroupedArgs g) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* tiles = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  __shared__ int src_row[BM];
+  pdl_trigger();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * TBN;
+  pdl_wait();
+  int z = blockIdx.z;
+  long long a_off = z * g.a_z, c_off = z * g.c_z;
+  if (g.tile_group != nullptr) {
+    z = g.tile_group[blockIdx.y];
+    if (z < 0) return;
+    a_off = c_off = 0;
+  }
+  const __nv_bfloat16* A = static_cast<const __nv_bfloat16*>(g.A) + a_off;
+  const __nv_bfloat16* W = static_cast<const __nv_bfloat16*>(g.W) + z * g.w_z;
+  const float* bias = g.bias ? g.bias + z * g.bias_z : nullptr;
+  TOut* C = static_cast<TOut*>(g.C) + c_off;
+  if (tid < BM) {
+    const int m = m0 + tid;
+    int r = m < g.M ? m : -1;
+    if (r >= 0 && g.row_index != nullptr) {
+      const int v = g.row_index[m];
+      r = v < 0 ? -1 : (g.gather ? v : m);
+    }
+    src_row[tid] = r;
+  }
+  __syncthreads();
+  // chunks of 8 halves: A has BM x 4 of them (one a thread), W has TBN x 4 (two a thread)
+  const int a_row = tid >> 2, a_chunk = (tid & 3) * 8;
+  const int a_src = src_row[a_row];
+  auto stage_load = [&](int stage, int k0) {
+    __nv_bfloat16* As = tiles + stage * TSTAGE_HALVES;
+    __nv_bfloat16* Ws = As + BM * TLD;
+    {
+      const int k = k0 + a_chunk;
+      const int bytes = a_src >= 0 ? max(0, min(16, (g.K - k) * 2)) : 0;
+      const __nv_bfloat16* src = bytes > 0 ? A + a_src * g.lda + k : A;
+      cp_async_16(As + a_row * TLD + a_chunk, src, bytes);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int c = tid + i * 256;
+      const int row = c >> 2, chunk = (c & 3) * 8;
+      const int n = n0 + row, k = k0 + chunk;
+      const int bytes = n < g.N ? max(0, min(16, (g.K - k) * 2)) : 0;
+      const __nv_bfloat16* src = bytes > 0 ? W + n * g.ldw + k : W;
+      cp_async_16(Ws + row * TLD + chunk, src, bytes);
+    }
+  };
+  const int wm = (warp >> 2) * 32, wn = (warp & 3) * 32;
+  float acc[2][4][4] = {};
+  const int k_tiles = (g.K + TBK - 1) / TBK;
+#pragma unroll
+  for (int s = 0; s < TSTAGES - 1; ++s) {
+    if (s < k_tiles) stage_load(s, s * TBK);
+    cp_async_commit();
+  }
+  for (int kt = 0; kt < k_tiles; ++kt) {
+    cp_async_wait<TSTAGES - 2>();
+    __syncthreads();
+    if (kt + TSTAGES - 1 < k_tiles) stage_load((kt + TSTAGES - 1) % TSTAGES, (kt + TSTAGES - 1) * TBK);
+    cp_async_commit();
+    const __nv_bfloat16* As = tiles + (kt % TSTAGES) * TSTAGE_HALVES;
+    const __nv_bfloat16* Ws = As + BM * TLD;
+#pragma unroll
+    for (int kk = 0; kk < TBK; kk += 16) {
+      uint32_t a[2][4], b[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+        ldmatrix_x4(a[i], As + (wm + i * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * TLD + kk + (lane >> 4) * 8);
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+        ldmatrix_x4(b[j], Ws + (wn + j * 16 + (lane & 7) + (lane >> 4) * 8) * TLD + kk + ((lane >> 3) & 1) * 8);
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) mma_bf16(acc[i][j], a[i], b[j >> 1][(j & 1) * 2], b[j >> 1][(j & 1) * 2 + 1]);
+    }
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int local = wm + i * 16 + (lane >> 2) + half * 8;
+      if (src_row[local] < 0) continue;
+      const long long m = m0 + local;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int n = n0 + wn + j * 8 + (lane & 3) * 2 + e;
+          if (n >= g.N) continue;
+          float v = acc[i][j][half * 2 + e] + (bias ? bias[n] : 0.f);
+          if (ACT == 1) {
+            v = fmaxf(v, 0.f);
+            v *= v;
+          }
+          C[m * g.ldc + n] = from_float<TOut>(v);
+        }
+    }
+}
+
+template <typename TOut>
+int launch_grouped_mma(const GroupedArgs& g, int batch, int act, cudaStream_t stream) {
+  dim3 grid((g.N + TBN - 1) / TBN, (g.M + BM - 1) / BM, batch);
+  if (grid.y > 65535 || grid.z > 65535) return B200_ERR_TOO_LARGE;
+  const size_t smem = sizeof(__nv_bfloat16) * TSTAGES * TSTAGE_HALVES;
+  if (act == 1) launch(grouped_gemm_mma_kernel<TOut, 1>, grid, dim3(256), smem, stream, g);
+  else launch(grouped_gemm_mma_kernel<TOut, 0>, grid, dim3(256), smem, stream, g);
+  return launch_status();
 }
 
 // ----------------------------------------------------------------------------- router
@@ -225,6 +352,16 @@ int launch_grouped(const GroupedArgs& g, int batch, int act, cudaStream_t stream
   return launch_status();
 }
 
+// LLM_RUNTIME_STUDY_B200_GROUPED=simt keeps bfloat16 products on the CUDA cores (for comparisons)
+inline bool use_tensor_cores() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("LLM_RUNTIME_STUDY_B200_GROUPED");
+    on = (e != nullptr && e[0] == 's') ? 0 : 1;
+  }
+  return on == 1;
+}
+
 }  // namespace b200
 
 // in_dtype: storage type of A and W; out_dtype: of C.  batch > 1 walks a_z / w_z / bias_z / c_z; with tile_group the
@@ -237,6 +374,12 @@ extern "C" int b200_gemm_grouped(const void* A, long long lda, long long a_z, co
   if (M <= 0 || N <= 0 || batch <= 0) return 0;
   if (K <= 0 || (tile_group != nullptr && batch != 1)) return B200_ERR_BAD_SIZE;
   GroupedArgs g{A, lda, a_z, row_index, gather, W, ldw, w_z, k_major, bias, bias_z, C, ldc, c_z, tile_group, M, N, K};
+  const bool aligned = ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) == 0 && lda % 8 == 0 && a_z % 8 == 0 &&
+                       ldw % 8 == 0 && w_z % 8 == 0;
+  if (in_dtype == kBF16 && aligned && !k_major && use_tensor_cores()) {
+    if (out_dtype == kBF16) return launch_grouped_mma<__nv_bfloat16>(g, batch, act, stream);
+    if (out_dtype == kF32) return launch_grouped_mma<float>(g, batch, act, stream);
+  }
   if (in_dtype == kF32 && out_dtype == kF32) return launch_grouped<float, float>(g, batch, act, stream);
   if (in_dtype == kBF16 && out_dtype == kBF16) return launch_grouped<__nv_bfloat16, __nv_bfloat16>(g, batch, act, stream);
   if (in_dtype == kBF16 && out_dtype == kF32) return launch_grouped<__nv_bfloat16, float>(g, batch, act, stream);

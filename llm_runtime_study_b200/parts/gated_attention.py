@@ -137,8 +137,8 @@ class LatentAttention(Mixer):
         self.kv_weight = None if self.shares_kv else runtime.place_vector_f32(tensors["dkv.norm"])
         self.uq_proj = Projection([tensors["uq"]], None, runtime)
         H = self.num_heads
-        # per head: [head_dim, kv_rank] read with k along its rows, and [value_dim, kv_rank]
-        self.uk = runtime.place_matrix(tensors["uk"]).view(H, self.head_dim, self.kv_rank)
+        # per head: W_uk^T as [kv_rank, head_dim] (the product with it is moved to the query's side), and W_uv [value_dim, kv_rank]
+        self.uk = runtime.place_matrix(tensors["uk"]).view(H, self.head_dim, self.kv_rank).transpose(1, 2).contiguous()
         self.uv = runtime.place_matrix(tensors["uv"]).view(H, self.value_dim, self.kv_rank)
         self.o_proj = Projection([tensors["o"]], None, runtime)
         if self.position is not None:
@@ -164,7 +164,7 @@ class LatentAttention(Mixer):
         n, H, row = q.shape[0], self.num_heads, self.kv_rank + self.rot_dim
         q_head = self.head_dim + self.rot_dim
         absorbed = torch.empty((n, H * row), dtype=q.dtype, device=q.device)
-        G.batched_linear(q, self.uk, batch=H, k=self.head_dim, n_out=self.kv_rank, a_batch_stride=q_head, weight_k_major=True,
+        G.batched_linear(q, self.uk, batch=H, k=self.head_dim, n_out=self.kv_rank, a_batch_stride=q_head,
                          out=absorbed, out_batch_stride=row)
         if self.rot_dim:
             M.rope_slice(q, absorbed, heads=H, src_head=q_head, src_offset=self.head_dim, dst_head=row, dst_offset=self.kv_rank,

@@ -320,6 +320,14 @@ def test_batched_products_with_strides():
     got = G.batched_linear(dev(a), dev(w.transpose(1, 2).contiguous()), batch=heads, k=k, n_out=n_out, a_batch_stride=25, weight_k_major=True)
     for h in range(heads):
         assert (got[:, h * n_out : (h + 1) * n_out].cpu().double() - a[:, h * 25 : h * 25 + k].double() @ w[h].double().T).abs().max() < 1e-4
+    # bfloat16 on the tensor cores (strides of whole 16-byte chunks) and on the CUDA cores (an odd stride)
+    for stride, kk in ((32, 24), (25, 20)):
+        ab = torch.randn(m, heads * stride).bfloat16()
+        wb = torch.randn(heads, n_out, kk).bfloat16()
+        got = G.batched_linear(dev(ab), dev(wb), batch=heads, k=kk, n_out=n_out, a_batch_stride=stride, out_dtype=torch.float32)
+        for h in range(heads):
+            want = ab[:, h * stride : h * stride + kk].double() @ wb[h].double().T
+            assert (got[:, h * n_out : (h + 1) * n_out].cpu().double() - want).abs().max() < 1e-3 * float(want.abs().max())
     # a row's bits do not depend on its company
     alone = G.batched_linear(dev(a[5:6].contiguous()), dev(w), batch=heads, k=k, n_out=n_out, a_batch_stride=25)
     among = G.batched_linear(dev(a), dev(w), batch=heads, k=k, n_out=n_out, a_batch_stride=25)

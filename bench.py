@@ -566,10 +566,10 @@ def _qwen3_like(width, ff, heads, kv_heads, d, pairs, vocab) -> dict:
     return cfg
 
 
-def run_sorulix(args) -> dict:
-    """Prefill and decode of Sorulix at layer sizes of real models (random weights), beside Qwen3 at equal width,
-    feed-forward, heads, head size and depth, through the same engine; then the new kernels alone, each against
-    the bytes or flops it must move, beside the kernel of the Qwen3 path that does the like work."""
+def _engine_measurer(args):
+    """(peaks, timed, measure) behind the workloads that set a design beside another at equal sizes: ``measure(cfg, vocab)``
+    opens an engine with seeded random weights and times a prefill of PREFILL_TOKENS tokens and decode steps at batch 1, 8
+    and 32 with CONTEXT cached tokens per request, from a CUDA graph."""
 
     import torch
 
@@ -636,6 +636,16 @@ def run_sorulix(args) -> dict:
         torch.cuda.empty_cache()
         return out
 
+    return peak, timed, measure
+
+
+def run_sorulix(args) -> dict:
+    """Prefill and decode of Sorulix at layer sizes of real models (random weights), beside Qwen3 at equal width,
+    feed-forward, heads, head size and depth, through the same engine; then the new kernels alone, each against
+    the bytes or flops it must move, beside the kernel of the Qwen3 path that does the like work."""
+
+    peak, timed, measure = _engine_measurer(args)
+    context = CONTEXT
     results = {}
     for name in (() if args.only == "kernels" else args.size.split(",") if args.size else SORULIX_SIZES):
         shape = SORULIX_SIZES[name]
@@ -752,6 +762,159 @@ def _sorulix_kernels(peak, timed) -> dict:
     return out
 
 
+# ------------------------------------------------------------------------------ Ropulix beside Sorulix and Qwen3
+ROPULIX_EXPERTS, ROPULIX_TOP, ROPULIX_WINDOW = 8, 2, 1024
+
+
+def _ropulix_config(width, ff, heads, kv_heads, d, pairs, vocab) -> dict:
+    """Four kinds of layers in turn (recurrence, latent attention, windowed attention, latent attention on borrowed rows);
+    every token uses ROPULIX_TOP experts whose hidden sizes add up to the dense feed-forward's."""
+
+    moe = {"kind": "moe", "expert": {"ff": ff // ROPULIX_TOP}, "router": {"experts": ROPULIX_EXPERTS, "top": ROPULIX_TOP}}
+    latent = {"heads": heads, "dim": d, "rot_dim": d // 2, "vdim": d, "kv_rank": 4 * d, "q_rank": width // 2, "mask": {"size": ROPULIX_WINDOW},
+              "rot": {"base": 10000.0, "dims": d // 2}, "scale": (d + d // 2) ** -0.5}
+    layers = []
+    for pair in range(pairs):
+        at = len(layers)
+        layers += [
+            {"type": "rglru", "mixer": {"width": width, "blocks": heads, "conv": 4}, "mlp": moe},
+            {"type": "latent_attention", "mixer": dict(latent), "mlp": moe},
+            {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": d, "vdim": d, "mask": {"size": ROPULIX_WINDOW},
+                                            "scale": d ** -0.5}, "mlp": moe},
+            {"type": "latent_attention", "mixer": dict(latent, kv_from=at + 1), "mlp": moe},
+        ]
+    return {"architecture": "Ropulix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "torch_dtype": "bfloat16",
+            "layers": layers[: 2 * pairs]}
+
+
+def run_ropulix(args) -> dict:
+    """Prefill and decode of Ropulix at layer sizes of real models (random weights), beside Sorulix (the closest design:
+    attention beside mixers with a state per request) and Qwen3 at equal width, active feed-forward size, heads, head size
+    and depth, through the same engine; then the new kernels alone against the bytes or flops they must move."""
+
+    peak, timed, measure = _engine_measurer(args)
+    results = {}
+    for name in (() if args.only == "kernels" else args.size.split(",") if args.size else SORULIX_SIZES):
+        shape = SORULIX_SIZES[name]
+        results[name] = {"shape": dict(zip(("width", "ff", "heads", "kv_heads", "head_dim", "layer_pairs", "vocab"), shape)),
+                         "experts": ROPULIX_EXPERTS, "top": ROPULIX_TOP, "window": ROPULIX_WINDOW,
+                         "ropulix": measure(_ropulix_config(*shape), shape[-1])}
+        if args.only not in ("prefill", "decode"):
+            results[name]["sorulix_equal_size"] = measure(_sorulix_config(*shape), shape[-1])
+            results[name]["qwen3_equal_size"] = measure(_qwen3_like(*shape), shape[-1])
+    kernels = _ropulix_kernels(peak, timed) if args.only in ("all", "kernels") else {}
+    return {"workload": "ropulix", "context": CONTEXT, "steps": args.steps, "warmup": max(args.warmup, 3), "dtype": "bfloat16",
+            "data": "synthetic token ids, seeded random weights", "peaks": peak, "models": results, "kernels": kernels}
+
+
+def _ropulix_kernels(peak, timed) -> dict:
+    """Each new kernel alone at the 4k shape (width 4096, 32 heads of 128), back to back, beside the kernel of an existing
+    path that does the like work."""
+
+    import torch
+    from types import SimpleNamespace
+
+    from llm_runtime_study_b200.ops import attention_latent
+    from llm_runtime_study_b200.ops import functional as F
+    from llm_runtime_study_b200.ops import gemm_bf16
+    from llm_runtime_study_b200.ops import grouped as G
+    from llm_runtime_study_b200.ops import mixer_steps as M
+    from llm_runtime_study_b200.ops import sequence_state as S
+
+    dev = "cuda:0"
+    width, heads, d, ff = 4096, 32, 128, 12288 // ROPULIX_TOP
+    out = {}
+    cold = timed
+
+    def timed(fn, repeat):
+        """Replayed from a CUDA graph, so that what is timed is the device's work and not the host's preparation of a launch of
+        a few microseconds; the first calls build and load libraries and make the maps a capture must not make."""
+
+        fn()
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fn()
+        graph.replay()
+        return cold(graph.replay, repeat)
+
+    bf = lambda *shape: (0.05 * torch.randn(*shape, device=dev)).bfloat16()
+    # experts: sorted rows through both products, against one dense projection of the same flops
+    router, up, down = torch.randn(ROPULIX_EXPERTS, width, device=dev), bf(ROPULIX_EXPERTS, ff, width), bf(ROPULIX_EXPERTS, width, ff)
+    for n in (2048, 8):
+        x = bf(n, width)
+        wide = G.wide_tiles_pay(n, ROPULIX_TOP, x.dtype, width, ff)
+        routing = G.route(x, router, None, top=ROPULIX_TOP, wide_tiles=wide)
+        hidden = G.expert_linear(x, up, routing, gather=True, act="relu2")
+        t_route = timed(lambda: G.route(x, router, None, top=ROPULIX_TOP, wide_tiles=wide), 10)
+        t_up = timed(lambda: G.expert_linear(x, up, routing, gather=True, act="relu2"), 10)
+        t_down = timed(lambda: G.expert_linear(hidden, down, routing, gather=False, out_dtype=torch.float32), 10)
+        rows = n * ROPULIX_TOP
+        dense_x, dense_w = bf(rows, width), bf(ff, width)
+        t_dense = timed(lambda: gemm_bf16.linear(dense_x, dense_w, None, torch.bfloat16) if rows >= 128
+                        else gemm_bf16.linear_skinny(dense_x, dense_w, None, torch.bfloat16), 10)
+        flops = 2.0 * rows * width * ff
+        touched = min(ROPULIX_EXPERTS, rows) * ff * width * 2
+        out[f"experts_{n}_tokens"] = {
+            "route_and_sort_us": round(t_route * 1e3, 1), "up_us": round(t_up * 1e3, 1), "down_us": round(t_down * 1e3, 1),
+            "dense_projection_of_equal_flops_us": round(t_dense * 1e3, 1),
+            "up_tflops": round(flops / t_up / 1e9, 1), "dense_tflops": round(flops / t_dense / 1e9, 1),
+            "of_measured_bf16_burst": {"up": round(flops / t_up / 1e9 / peak["bf16_tflops"], 3), "dense": round(flops / t_dense / 1e9 / peak["bf16_tflops"], 3)},
+            "of_measured_copy": {"up": round(touched / t_up / 1e6 / peak["hbm_gbs"], 3), "dense": round(ff * width * 2 / t_dense / 1e6 / peak["hbm_gbs"], 3)}}
+    # latent attention over shared rows (CUDA cores) beside the plain windowed attention of equal heads (tensor cores)
+    rank, rot, page = 4 * d, d // 2, PAGE_SIZE
+    for n, new in ((2048, 2048), (8 * 2048, 8)):
+        length = 2048
+        seqs = n // length if new == n else 8
+        lengths = [length] * seqs
+        q_lens = [length] * seqs if new == n else [1] * seqs
+        pages = sum(-(-m // page) for m in lengths)
+        table = torch.arange(pages, dtype=torch.int32).view(seqs, -1).to(dev)
+        pool = bf(pages, page, rank + rot)
+        q = bf(sum(q_lens), heads, rank + rot)
+        positions = torch.cat([torch.arange(m - k, m) for m, k in zip(lengths, q_lens)]).int().to(dev)
+        entry = torch.cat([torch.full((k,), i) for i, k in enumerate(q_lens)]).int().to(dev)
+        ctx = SimpleNamespace(positions=positions, token_entry=entry, all_decode=max(q_lens) == 1, num_entries=seqs, q_lens=q_lens,
+                              kv_lens=lengths)
+        t = timed(lambda: attention_latent.latent_attention(q, pool, ctx, table, value_dim=rank, scale=0.07, window=ROPULIX_WINDOW), 3)
+        t_simt = cold(lambda: F.paged_attention_simt_latent(q, pool, value_dim=rank, positions=positions, token_entry=entry,
+                                                            block_table=table, scale=0.07, window=ROPULIX_WINDOW), 1)
+        seen = sum(min(ROPULIX_WINDOW, p + 1) for p in positions.tolist())
+        flops = 2.0 * heads * seen * (2 * rank + rot)
+        out[f"latent_attention_{'prefill' if new == n else 'decode_b8'}_{length}"] = {
+            "ms": round(t, 3), "cuda_core_kernel_ms": round(t_simt, 3), "tflops": round(flops / t / 1e9, 2),
+            "of_measured_bf16_burst": round(flops / t / 1e9 / peak["bf16_tflops"], 4),
+            "rows_read_mb": round(seqs * min(length, ROPULIX_WINDOW + (length if new == n else 0)) * (rank + rot) * 2 / 1e6, 2)}
+    # the recurrence: a prompt portion is a chain per channel; decoding moves the state in and out
+    for n, entries in ((2048, 1), (32, 32)):
+        bw = width // heads
+        proj, u = bf(n, 2 * width), bf(n, width)
+        gates = torch.randn(n, heads, 2 * bw, device=dev)
+        lam = torch.randn(width, device=dev)
+        state = torch.zeros(entries + 1, width, device=dev)
+        q_start = torch.arange(0, n + 1, n // entries, dtype=torch.int32, device=dev)
+        slots = torch.arange(entries, dtype=torch.int32, device=dev)
+        gate_w = bf(heads, 2 * bw, bw)
+        t_scan = timed(lambda: M.gated_recurrence(gates, u, proj, y_offset=width, lam=lam, decay_scale=8.0, state=state, q_start=q_start,
+                                                  slots=slots, block_width=bw), 5)
+        t_gates = timed(lambda: G.batched_linear(u, gate_w, batch=heads, k=bw, n_out=2 * bw, a_batch_stride=bw, out_dtype=torch.float32), 5)
+        moved = n * width * (8 + 2 + 2 + 2)
+        out[f"recurrence_{n}_tokens_{entries}_requests"] = {
+            "scan_us": round(t_scan * 1e3, 1), "gate_product_us": round(t_gates * 1e3, 1),
+            "scan_of_measured_copy": round(moved / t_scan / 1e6 / peak["hbm_gbs"], 3),
+            "gate_product_tflops": round(2.0 * n * width * 2 * bw / t_gates / 1e9, 1)}
+    # the norm on a sublayer's output beside the pre-norm's add-and-normalise
+    rows = 2048
+    x, w, resid = torch.randn(rows, width, device=dev), torch.randn(width, device=dev), torch.randn(rows, width, device=dev)
+    t_new = timed(lambda: M.norm_accumulate_round(x, w, 1e-6, resid, torch.bfloat16), 20)
+    t_old = timed(lambda: F.add_rmsnorm(resid, x, w, 1e-6, torch.bfloat16), 20)
+    out["norm_on_output_2048x4096"] = {"us": round(t_new * 1e3, 1), "add_rmsnorm_us": round(t_old * 1e3, 1),
+                                       "of_measured_copy": {"norm_on_output": round(rows * width * 14 / t_new / 1e6 / peak["hbm_gbs"], 3),
+                                                            "add_rmsnorm": round(rows * width * 14 / t_old / 1e6 / peak["hbm_gbs"], 3)}}
+    return out
+
+
 def run_reference(args) -> dict:
     """The unmodified reference from baseline/_ref: its own Qwen3ForCausalLM, paged cache,
     CUDA-graph decode and BatchScheduler, driven through Engine.create_scheduler()."""
@@ -855,10 +1018,11 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--context", type=int, default=0, help="with --only decode: cached tokens per request (default 2048)")
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (named in config)")
-    parser.add_argument("--workload", choices=("default", "staggered14b", "decode32b", "sorulix"), default="default",
+    parser.add_argument("--workload", choices=("default", "staggered14b", "decode32b", "sorulix", "ropulix"), default="default",
                         help="default: Qwen3-8B decode/prefill; staggered14b, decode32b: the larger configurations (either --impl); "
-                             "sorulix: the Sorulix design beside Qwen3 at equal sizes, and its kernels alone")
-    parser.add_argument("--size", default="", help="with --workload sorulix: sizes to run, with commas (2k, 4k; default both)")
+                             "sorulix: the Sorulix design beside Qwen3 at equal sizes, and its kernels alone; "
+                             "ropulix: the Ropulix design beside Sorulix and Qwen3 at equal sizes, and its kernels alone")
+    parser.add_argument("--size", default="", help="with --workload sorulix or ropulix: sizes to run, with commas (2k, 4k; default both)")
     parser.add_argument("--only", choices=("all", "decode", "prefill", "kernels", "models"), default="all",
                         help="run only the decode steps or only the prefill (for profiler captures of a small case); "
                              "with --workload sorulix: only the kernels alone, or only the whole models")
@@ -875,6 +1039,11 @@ def main() -> int:
             result = _unavailable("the reference has no model of this design")
         else:
             result = run_sorulix(args)
+    elif args.workload == "ropulix":
+        if args.impl == "reference":
+            result = _unavailable("the reference has no model of this design")
+        else:
+            result = run_ropulix(args)
     else:
         result = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(result))

@@ -21,6 +21,7 @@ struct GroupedArgs {
   const float* bias; long long bias_z;
   void* C; long long ldc, c_z;
   const int* tile_group;                    // per row tile: the group (expert) whose weight it uses, < 0: nothing to do
+  int group_tile_rows;                      // rows of the tiles tile_group speaks of (a multiple of BM)
   int M, N, K;
 };
 
@@ -37,7 +38,7 @@ grouped_gemm_kernel(const GroupedArgs g) {
   int z = blockIdx.z;
   long long a_off = z * g.a_z, c_off = z * g.c_z;
   if (g.tile_group != nullptr) {
-    z = g.tile_group[blockIdx.y];
+    z = g.tile_group[blockIdx.y * BM / g.group_tile_rows];
     if (z < 0) return;
     a_off = c_off = 0;
   }
@@ -123,7 +124,7 @@ grouped_gemm_mma_kernel(const GroupedArgs g) {
   int z = blockIdx.z;
   long long a_off = z * g.a_z, c_off = z * g.c_z;
   if (g.tile_group != nullptr) {
-    z = g.tile_group[blockIdx.y];
+    z = g.tile_group[blockIdx.y * BM / g.group_tile_rows];
     if (z < 0) return;
     a_off = c_off = 0;
   }
@@ -242,12 +243,22 @@ route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float*
   if (token >= n) return;
   float* logits = logits_all + warp * experts;
   const T* row = h + static_cast<size_t>(token) * width;
-  for (int e = 0; e < experts; ++e) {
-    const float* w = wr + static_cast<size_t>(e) * width;
-    float dot = 0.f;
-    for (int i = lane; i < width; i += 32) dot = fmaf(to_float(row[i]), w[i], dot);
-    dot = warp_sum(dot);
-    if (lane == 0) logits[e] = dot + (br ? br[e] : 0.f);
+  // eight experts per pass over the row: eight independent sums, each formed in the same order as one alone would be
+  for (int e0 = 0; e0 < experts; e0 += 8) {
+    float dot[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dot[j] = 0.f;
+    for (int i = lane; i < width; i += 32) {
+      const float x = to_float(row[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (e0 + j < experts) dot[j] = fmaf(x, wr[static_cast<size_t>(e0 + j) * width + i], dot[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float total_j = warp_sum(dot[j]);
+      if (lane == 0 && e0 + j < experts) logits[e0 + j] = total_j + (br ? br[e0 + j] : 0.f);
+    }
   }
   __syncwarp();
   float first = 0.f, total = 0.f, mine = 0.f;
@@ -281,17 +292,17 @@ route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float*
 
 // One CTA.  Counts the pairs of every expert, lays the experts' rows out one behind the other, each padded to whole
 // tiles of BM rows, and gives every pair its row: sorted_token[row] = token (-1 in the padding), pair_row[pair] = row,
-// tile_group[tile] = expert (-1 behind the last used tile).
+// tile_group[tile] = expert (-1 behind the last used tile).  A tile has tile_rows rows (what the product kernel takes).
 __global__ void __launch_bounds__(1024)
 plan_kernel(const int* __restrict__ ids, int pairs, int top, int experts, int* __restrict__ sorted_token, int* __restrict__ pair_row,
-            int* __restrict__ tile_group, int max_tiles) {
+            int* __restrict__ tile_group, int max_tiles, int tile_rows) {
   extern __shared__ int sh[];
   int* count = sh;                 // [experts]
   int* start = sh + experts;       // [experts + 1], in rows
   pdl_trigger();
   pdl_wait();
   for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
-  for (int r = threadIdx.x; r < max_tiles * BM; r += blockDim.x) sorted_token[r] = -1;
+  for (int r = threadIdx.x; r < max_tiles * tile_rows; r += blockDim.x) sorted_token[r] = -1;
   __syncthreads();
   for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&count[ids[p]], 1);
   __syncthreads();
@@ -299,14 +310,14 @@ plan_kernel(const int* __restrict__ ids, int pairs, int top, int experts, int* _
     int at = 0;
     for (int e = 0; e < experts; ++e) {
       start[e] = at;
-      at += (count[e] + BM - 1) / BM * BM;
+      at += (count[e] + tile_rows - 1) / tile_rows * tile_rows;
       count[e] = 0;
     }
     start[experts] = at;
   }
   __syncthreads();
   for (int t = threadIdx.x; t < max_tiles; t += blockDim.x) {
-    const int row = t * BM;
+    const int row = t * tile_rows;
     int group = -1;
     if (row < start[experts]) {
       int lo = 0, hi = experts - 1;          // the last expert whose start is <= row and that has rows
@@ -343,6 +354,15 @@ combine_kernel(const float* __restrict__ rows, const int* __restrict__ pair_row,
   }
 }
 
+__global__ void __launch_bounds__(128)
+gather_rows_kernel(const uint4* __restrict__ x, const int* __restrict__ sorted_token, uint4* __restrict__ out, int chunks) {
+  pdl_trigger();
+  pdl_wait();
+  const int src = sorted_token[blockIdx.x];
+  for (int i = threadIdx.x; i < chunks; i += blockDim.x)
+    out[static_cast<size_t>(blockIdx.x) * chunks + i] = src >= 0 ? x[static_cast<size_t>(src) * chunks + i] : make_uint4(0, 0, 0, 0);
+}
+
 template <typename TIn, typename TOut>
 int launch_grouped(const GroupedArgs& g, int batch, int act, cudaStream_t stream) {
   dim3 grid((g.N + BN - 1) / BN, (g.M + BM - 1) / BM, batch);
@@ -365,15 +385,15 @@ inline bool use_tensor_cores() {
 }  // namespace b200
 
 // in_dtype: storage type of A and W; out_dtype: of C.  batch > 1 walks a_z / w_z / bias_z / c_z; with tile_group the
-// weight of a row tile is W + tile_group[tile] * w_z instead (batch must be 1).  act: 0 none, 1 relu squared.
+// weight of a row tile is W + tile_group[tile] * w_z instead (batch must be 1; tile_group speaks of tiles of group_tile_rows rows).  act: 0 none, 1 relu squared.
 extern "C" int b200_gemm_grouped(const void* A, long long lda, long long a_z, const int* row_index, int gather, const void* W,
                                  long long ldw, long long w_z, int k_major, const float* bias, long long bias_z, void* C,
-                                 long long ldc, long long c_z, const int* tile_group, int M, int N, int K, int batch, int act,
-                                 int in_dtype, int out_dtype, cudaStream_t stream) {
+                                 long long ldc, long long c_z, const int* tile_group, int group_tile_rows, int M, int N, int K, int batch,
+                                 int act, int in_dtype, int out_dtype, cudaStream_t stream) {
   using namespace b200;
   if (M <= 0 || N <= 0 || batch <= 0) return 0;
-  if (K <= 0 || (tile_group != nullptr && batch != 1)) return B200_ERR_BAD_SIZE;
-  GroupedArgs g{A, lda, a_z, row_index, gather, W, ldw, w_z, k_major, bias, bias_z, C, ldc, c_z, tile_group, M, N, K};
+  if (K <= 0 || (tile_group != nullptr && (batch != 1 || group_tile_rows <= 0 || group_tile_rows % BM != 0))) return B200_ERR_BAD_SIZE;
+  GroupedArgs g{A, lda, a_z, row_index, gather, W, ldw, w_z, k_major, bias, bias_z, C, ldc, c_z, tile_group, group_tile_rows, M, N, K};
   const bool aligned = ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) == 0 && lda % 8 == 0 && a_z % 8 == 0 &&
                        ldw % 8 == 0 && w_z % 8 == 0;
   if (in_dtype == kBF16 && aligned && !k_major && use_tensor_cores()) {
@@ -400,12 +420,22 @@ extern "C" int b200_moe_route(const void* h, const float* wr, const float* br, i
 extern "C" int b200_moe_tile_rows() { return b200::BM; }
 
 extern "C" int b200_moe_plan(const int* ids, int pairs, int top, int experts, int* sorted_token, int* pair_row, int* tile_group,
-                             int max_tiles, cudaStream_t stream) {
+                             int max_tiles, int tile_rows, cudaStream_t stream) {
   using namespace b200;
   if (pairs <= 0) return 0;
-  if (experts <= 0 || experts > 2048 || top <= 0 || max_tiles * BM < pairs) return B200_ERR_BAD_SIZE;
+  if (experts <= 0 || experts > 2048 || top <= 0 || tile_rows <= 0 || tile_rows % BM != 0 || max_tiles * tile_rows < pairs) return B200_ERR_BAD_SIZE;
   launch(plan_kernel, dim3(1), dim3(1024), sizeof(int) * (2 * experts + 1), stream, ids, pairs, top, experts, sorted_token, pair_row,
-         tile_group, max_tiles);
+         tile_group, max_tiles, tile_rows);
+  return launch_status();
+}
+
+// out[row] = x[sorted_token[row]] (zeros where the row is padding): the rows of every expert one behind the other, for a
+// product kernel that fetches its row operand by TMA.  width is a multiple of 8.
+extern "C" int b200_gather_rows_bf16(const void* x, const int* sorted_token, void* out, int rows, int width, cudaStream_t stream) {
+  using namespace b200;
+  if (rows <= 0) return 0;
+  if (width <= 0 || width % 8 != 0) return B200_ERR_BAD_SIZE;
+  launch(gather_rows_kernel, dim3(rows), dim3(128), 0, stream, static_cast<const uint4*>(x), sorted_token, static_cast<uint4*>(out), width / 8);
   return launch_status();
 }
 

@@ -104,6 +104,11 @@ struct GemmParams {
   int splits;         // split-K: CTAs (one cluster) that share the K range of a tile, at most 8
   int a_rows;         // split-K: rows of the row operand's box, a multiple of 8 up to 128
   int bn, stages;     // split-K: columns per tile (a multiple of 32, at most 256), stages of the operand ring
+  // persistent kernel, rows in groups (each 128-row tile belongs to one group, whose weight is rows
+  // group * group_rows .. of the column operand): the group of every row tile, < 0 for a tile without work
+  const int* tile_group;
+  int group_rows;
+  int act;            // 1: the square of relu on the way out (not with SWIGLU)
 };
 
 // What the epilogue does with 32 consecutive accumulator columns of one row, starting at column nb of
@@ -114,6 +119,13 @@ __device__ __forceinline__ void finish_chunk(float (&v)[32], const GemmParams& p
   if (p.bias) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] += nb + j < p.N ? p.bias[nb + j] : 0.f;
+  }
+  if (p.act == 1) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const float r = fmaxf(v[j], 0.f);
+      v[j] = r * r;
+    }
   }
   if constexpr (SWIGLU) {
     // [g0..7 | u0..7 | g8..15 | u8..15] -> 16 outputs at column nb / 2 (N is a multiple of 16)
@@ -219,7 +231,13 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_rows, con
     uint32_t phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-      const int row0 = (tile % m_tiles) * BM, col0 = (tile / m_tiles) * BN;
+      const int row0 = (tile % m_tiles) * BM;
+      int col0 = (tile / m_tiles) * BN;
+      if (p.tile_group != nullptr) {
+        const int group = p.tile_group[tile % m_tiles];
+        if (group < 0) continue;
+        col0 += group * p.group_rows;
+      }
       for (int kb = 0; kb < num_kb; ++kb) {
         if (!mbar_wait_warp(empty + s, phase ^ 1)) { atomicExch(&g_gemm_error, 1); ok = false; break; }
         unsigned char* stage = smem + s * STAGE_BYTES;
@@ -238,9 +256,11 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_rows, con
     int s = 0, local = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
+    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+      if (p.tile_group != nullptr && p.tile_group[tile % m_tiles] < 0) continue;
       const int buf = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
+      ++local;
       if (!mbar_wait_warp(acc_empty + buf, acc_phase ^ 1)) { atomicExch(&g_gemm_error, 4); ok = false; break; }
       tcgen05_fence_after();
       const uint32_t tmem_d = tmem_base + buf * BN;
@@ -265,9 +285,11 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_rows, con
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     int local = 0;
-    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
+    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+      if (p.tile_group != nullptr && p.tile_group[tile % m_tiles] < 0) continue;
       const int buf = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
+      ++local;
       const int row0 = (tile % m_tiles) * BM, col0 = (tile / m_tiles) * BN;
       const bool ok = mbar_wait(acc_full + buf, acc_phase);
       if (!ok) atomicExch(&g_gemm_error, 3);
@@ -1196,4 +1218,23 @@ extern "C" int b200_gemm_tcgen05(const void* A, const void* W, const float* bias
   }
   if (tile_n == 128) return launch_variant<0, 128>(rows, cols, p, out_f32, swiglu, stream);
   return launch_variant<0, 256>(rows, cols, p, out_f32, swiglu, stream);
+}
+
+// Rows in groups: A [M, K] holds the rows of group after group, each group padded to whole tiles of 128 rows
+// (tile_group[t]: the group of row tile t, < 0: nothing to do); W is [groups * N, K], group g's weight its rows
+// g * N ..; C [M, N] (+ row stride ldc).  act 1: the square of relu on the way out.  The persistent kernel.
+extern "C" int b200_gemm_tcgen05_grouped(const void* A, const void* W, void* C, int M, int N, int K, int ldc, int out_f32, int act,
+                                         const int* tile_group, int groups, int tile_n, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || groups <= 0) return 0;
+  if (K <= 0 || K % 8 != 0 || ldc < N || M % BM != 0 || tile_group == nullptr || (tile_n != 128 && tile_n != 256)) return B200_ERR_BAD_SIZE;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) return B200_ERR_BAD_SIZE;
+  GemmParams p{C, nullptr, M, N, K, ldc, (ldc % 8 == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0, 0, nullptr, nullptr, 1, BM, tile_n, 0};
+  p.tile_group = tile_group;
+  p.group_rows = N;
+  p.act = act;
+  CUtensorMap rows, cols;
+  if (int e = make_map(&rows, A, M, K, BM)) return e;
+  if (int e = make_map(&cols, W, groups * N, K, tile_n)) return e;
+  if (tile_n == 128) return launch_variant<0, 128>(rows, cols, p, out_f32, 0, stream);
+  return launch_variant<0, 256>(rows, cols, p, out_f32, 0, stream);
 }

@@ -42,34 +42,67 @@ __device__ __forceinline__ float gelu_tanh(float z) {
   return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
-// One thread per (entry, channel) walks the entry's tokens in order.  gates: float32 [n, blocks, 2 * bw] (r logits, then i
-// logits, of the block's channels); y: column y_off + c of the projection rows; state [slots, width].
+// The gates' arithmetic for every (token, channel) at once, all of it independent of the state: a = exp(-c r softplus(lam)),
+// b = sqrt(1 - a^2) i u, and gelu_tanh(y) in the activation type.  gates: float32 [n, blocks, 2 * bw] (r logits, then i
+// logits, of the block's channels); y: column y_off + c of the projection rows.
+template <typename T>
+__global__ void __launch_bounds__(256)
+recurrence_inputs_kernel(const float* __restrict__ gates, const T* __restrict__ u, const T* __restrict__ proj, int ld, int y_off,
+                         const float* __restrict__ lam, float decay_scale, float* __restrict__ a_out, float* __restrict__ b_out,
+                         T* __restrict__ y_out, int width, int bw) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= width) return;
+  const float lm = lam[c];
+  const float sp = lm > 20.f ? lm : log1pf(expf(lm));
+  const int block = c / bw, o = c - block * bw;
+  const float* g = gates + (static_cast<size_t>(t) * (width / bw) + block) * 2 * bw;
+  const float r = 1.f / (1.f + expf(-g[o]));
+  const float i = 1.f / (1.f + expf(-g[bw + o]));
+  const float log_a = -decay_scale * r * sp;
+  const size_t at = static_cast<size_t>(t) * width + c;
+  a_out[at] = expf(log_a);
+  b_out[at] = sqrtf(-expm1f(2.f * log_a)) * i * to_float(u[at]);
+  y_out[at] = from_float<T>(gelu_tanh(to_float(proj[static_cast<size_t>(t) * ld + y_off + c])));
+}
+
+// One thread per (entry, channel) walks the entry's tokens in order: S <- a S + b, out = S * y.  Only the multiply-adds form
+// a chain; the loads of sixteen tokens are in flight together.  state [slots, width]; y is read and the result written in place.
 template <typename T>
 __global__ void __launch_bounds__(128)
-gated_recurrence_kernel(const float* __restrict__ gates, const T* __restrict__ u, const T* __restrict__ proj, int ld, int y_off,
-                        const float* __restrict__ lam, float decay_scale, float* __restrict__ state,
-                        const int* __restrict__ q_start, const int* __restrict__ slots, T* __restrict__ out, int width, int bw) {
+gated_recurrence_kernel(const float* __restrict__ a, const float* __restrict__ b, T* __restrict__ y, float* __restrict__ state,
+                        const int* __restrict__ q_start, const int* __restrict__ slots, int width) {
   pdl_trigger();
   pdl_wait();
   const int entry = blockIdx.y;
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= width) return;
   const int first = q_start[entry], last = q_start[entry + 1];
-  const float lm = lam[c];
-  const float sp = lm > 20.f ? lm : log1pf(expf(lm));
-  const int block = c / bw, o = c % bw;
   float* st = state + static_cast<size_t>(slots[entry]) * width + c;
   float S = *st;
-  for (int t = first; t < last; ++t) {
-    const float* g = gates + (static_cast<size_t>(t) * (width / bw) + block) * 2 * bw;
-    const float r = 1.f / (1.f + expf(-g[o]));
-    const float i = 1.f / (1.f + expf(-g[bw + o]));
-    const float log_a = -decay_scale * r * sp;
-    const float a = expf(log_a);
-    const float in = sqrtf(-expm1f(2.f * log_a)) * i * to_float(u[static_cast<size_t>(t) * width + c]);
-    S = fmaf(a, S, in);
-    const float y = gelu_tanh(to_float(proj[static_cast<size_t>(t) * ld + y_off + c]));
-    out[static_cast<size_t>(t) * width + c] = from_float<T>(S * y);
+  constexpr int U = 16;
+  int t0 = first;
+  for (; t0 + U <= last; t0 += U) {
+    float av[U], bv[U], yv[U];
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+      const size_t at = static_cast<size_t>(t0 + j) * width + c;
+      av[j] = a[at];
+      bv[j] = b[at];
+      yv[j] = to_float(y[at]);
+    }
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+      S = fmaf(av[j], S, bv[j]);
+      y[static_cast<size_t>(t0 + j) * width + c] = from_float<T>(S * yv[j]);
+    }
+  }
+  for (; t0 < last; ++t0) {
+    const size_t at = static_cast<size_t>(t0) * width + c;
+    S = fmaf(a[at], S, b[at]);
+    y[at] = from_float<T>(S * to_float(y[at]));
   }
   *st = S;
 }
@@ -89,16 +122,22 @@ extern "C" int b200_conv_taps(const void* proj, int ld, const float* taps, const
   return launch_status();
 }
 
+// gates float32 [n, width / bw, 2 * bw]; u [n, width] and proj rows in the activation type; a_scratch, b_scratch float32 [n, width];
+// out [n, width] in the activation type.
 extern "C" int b200_gated_recurrence(const float* gates, const void* u, const void* proj, int ld, int y_off, const float* lam,
-                                     float decay_scale, float* state, const int* q_start, const int* slots, void* out, int entries,
-                                     int width, int bw, int dtype, cudaStream_t stream) {
+                                     float decay_scale, float* state, const int* q_start, const int* slots, void* out,
+                                     float* a_scratch, float* b_scratch, int n, int entries, int width, int bw, int dtype,
+                                     cudaStream_t stream) {
   using namespace b200;
-  if (entries <= 0) return 0;
+  if (entries <= 0 || n <= 0) return 0;
   if (width <= 0 || bw <= 0 || width % bw != 0 || ld < y_off + width) return B200_ERR_BAD_SIZE;
-  dim3 grid((width + 127) / 128, entries);
-  if (grid.y > 65535) return B200_ERR_TOO_LARGE;
-  B200_DISPATCH_DTYPE(dtype, T, launch(gated_recurrence_kernel<T>, grid, dim3(128), 0, stream, gates, static_cast<const T*>(u),
-                                       static_cast<const T*>(proj), ld, y_off, lam, decay_scale, state, q_start, slots,
-                                       static_cast<T*>(out), width, bw));
+  dim3 wide(n, (width + 255) / 256), grid((width + 127) / 128, entries);
+  if (grid.y > 65535 || wide.y > 65535) return B200_ERR_TOO_LARGE;
+  B200_DISPATCH_DTYPE(dtype, T, {
+    launch(recurrence_inputs_kernel<T>, wide, dim3(256), 0, stream, gates, static_cast<const T*>(u), static_cast<const T*>(proj), ld,
+           y_off, lam, decay_scale, a_scratch, b_scratch, static_cast<T*>(out), width, bw);
+    launch(gated_recurrence_kernel<T>, grid, dim3(128), 0, stream, a_scratch, b_scratch, static_cast<T*>(out), state, q_start, slots,
+           width);
+  });
   return launch_status();
 }

@@ -1,0 +1,76 @@
+"""Choice of the kernel for attention over one shared row per token (latent attention with the up-projections moved
+to the query's side)."""
+
+from __future__ import annotations
+
+import os
+from typing import Any
+
+import torch
+
+from . import attention_bf16, native
+from . import functional as F
+from .native import c_float, c_int, c_void_p
+
+# "mma": the tensor-core kernel wherever it takes the sizes; "simt": the CUDA-core kernel everywhere
+BACKEND = os.environ.get("LLM_RUNTIME_STUDY_B200_ATTENTION_LATENT", "mma")
+ROWS_PER_TILE = 64
+MAX_SHARED_BYTES = 227 * 1024
+
+_TABLE = {
+    "b200_attention_latent_rank": [],
+    "b200_attention_latent_rot": [],
+    "b200_attention_latent_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int,
+                                   c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+}
+
+
+def library_name(rank: int, rot: int) -> str:
+    name = f"b200_attention_latent_r{rank}_t{rot}"
+    if name not in native.library_specs():
+        native.register_library(name, ("attention_latent.cu",), _TABLE, defines=(f"LATENT_RANK={rank}", f"LATENT_ROT={rot}"))
+    return name
+
+
+def supported(rank: int, rot: int) -> bool:
+    """Both widths in steps of 16, values of at most 512 columns, and two key tiles beside the query tile in shared memory."""
+
+    return (rank % 16 == 0 and rot % 16 == 0 and 16 <= rank <= 512 and rot >= 0
+            and (ROWS_PER_TILE + 64) * (rank + rot + 8) * 2 <= MAX_SHARED_BYTES)
+
+
+def build(rank: int, rot: int) -> None:
+    from ..csrc.build import build_library
+
+    name = library_name(rank, rot)
+    build_library(name, ("attention_latent.cu",), native.library_defines(name))
+
+
+def latent_attention(q: torch.Tensor, pool: torch.Tensor, ctx: Any, table: torch.Tensor, *, value_dim: int, scale: float,
+                     window: int = 0) -> torch.Tensor:
+    """Causal attention of the batch's query tokens ``[N, heads, d]`` over their requests' rows ``[pages, page_size, d]``,
+    whose first ``value_dim`` columns are the values; result ``[N, heads, value_dim]``.
+
+    bfloat16 with both widths in steps of 16: the mma.sync kernel (prompt portions and single tokens alike: a tile is up to
+    ``64 // heads`` consecutive tokens of one request times the heads).  float32, and every other size: the CUDA-core kernel."""
+
+    n, heads, d = q.shape
+    rot = d - value_dim
+    if BACKEND != "mma" or q.dtype != torch.bfloat16 or not supported(value_dim, rot):
+        return F.paged_attention_simt_latent(q, pool, value_dim=value_dim, positions=ctx.positions, token_entry=ctx.token_entry,
+                                             block_table=table, scale=scale, window=window)
+    per_tile = max(1, ROWS_PER_TILE // heads)
+    maps = ctx.__dict__.setdefault("_tile_maps", {})
+    key = ("latent", per_tile)
+    if key not in maps:
+        if ctx.all_decode and n == ctx.num_entries:
+            ramp = torch.arange(n, dtype=torch.int32, device=q.device)      # one tile a request, made on the device
+            maps[key] = ((ramp, ramp, torch.ones_like(ramp)), n)
+        else:
+            maps[key] = attention_bf16.tile_map(ctx.q_lens, per_tile, q.device, ctx.kv_lens)
+    tiles, count = maps[key]
+    out = torch.empty((n, heads, value_dim), dtype=q.dtype, device=q.device)
+    native.call("b200_attention_latent_bf16", q.data_ptr(), pool.data_ptr(), out.data_ptr(), ctx.positions.data_ptr(), table.data_ptr(),
+                table.shape[1], pool.shape[1], heads, float(scale), int(window), tiles[0].data_ptr(), tiles[1].data_ptr(),
+                tiles[2].data_ptr(), count, native.stream_ptr(), library=library_name(value_dim, rot))
+    return out

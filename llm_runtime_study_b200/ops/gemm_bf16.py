@@ -15,6 +15,8 @@ native.register_library(
     {
         "b200_gemm_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                               c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+        "b200_gemm_tcgen05_grouped": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int,
+                                      c_void_p],
         "b200_gemm_tcgen05_error": [],
         "b200_gemm_tcgen05_splitk_shape": [c_int, c_int, c_int, c_int, c_void_p, c_void_p],
         "b200_gemm_tcgen05_streamk_partial_floats": [],

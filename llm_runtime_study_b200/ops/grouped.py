@@ -4,12 +4,20 @@ the worst case and tiles without rows leave at once, so a step can be replayed f
 
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 
 import torch
 
 from ..errors import KernelError
 from .native import call, ptr, query, require, stream_ptr, tag
+
+# Rows of (token, choice) pairs from which the experts' products go to the tcgen05 kernel (tiles of 128 rows an expert);
+# below that, and wherever a width is no multiple of eight, the mma.sync kernel with tiles of 64 rows.
+# LLM_RUNTIME_STUDY_B200_EXPERTS=mma keeps every size on the latter.
+TC_MIN_PAIRS = 512
+TC_TILE_ROWS = 128
+EXPERTS_BACKEND = os.environ.get("LLM_RUNTIME_STUDY_B200_EXPERTS", "tcgen05")
 
 
 def batched_linear(
@@ -42,7 +50,7 @@ def batched_linear(
         if out_batch_stride is None or (batch - 1) * out_batch_stride + n_out > out.shape[1]:
             raise KernelError("batched_linear: a batch entry's results lie outside out")
     call("b200_gemm_grouped", ptr(a), a.stride(0), a_batch_stride, None, 0, ptr(weight), weight.stride(1), weight.stride(0),
-         1 if weight_k_major else 0, ptr(bias), n_out, out.data_ptr(), out.stride(0), out_batch_stride, None, m, n_out, k, batch, 0,
+         1 if weight_k_major else 0, ptr(bias), n_out, out.data_ptr(), out.stride(0), out_batch_stride, None, 0, m, n_out, k, batch, 0,
          tag(a.dtype), tag(out.dtype), stream_ptr())
     return out
 
@@ -59,6 +67,7 @@ class Routing:
     sorted_token: torch.Tensor
     tile_group: torch.Tensor
     top: int
+    tile_rows: int = 64
 
     @property
     def rows(self) -> int:
@@ -69,10 +78,10 @@ def tile_rows() -> int:
     return query("b200_moe_tile_rows")
 
 
-def route(h: torch.Tensor, router: torch.Tensor, bias: torch.Tensor | None, *, top: int) -> Routing:
+def route(h: torch.Tensor, router: torch.Tensor, bias: torch.Tensor | None, *, top: int, wide_tiles: bool = False) -> Routing:
     """Logits ``router @ h + bias`` in float32 (``router`` float32 ``[experts, width]``; ``h`` in the activation type), the ``top``
     largest chosen (the lower index wins a tie), weights the softmax over the chosen logits; then the pairs sorted by expert,
-    each expert's rows padded to whole tiles."""
+    each expert's rows padded to whole tiles (of 128 rows with ``wide_tiles``, what the tcgen05 kernel takes; else of 64)."""
 
     require(h, "h", dims=2)
     n, width = h.shape
@@ -86,20 +95,39 @@ def route(h: torch.Tensor, router: torch.Tensor, bias: torch.Tensor | None, *, t
     ids = torch.empty((n, top), dtype=torch.int32, device=dev)
     weights = torch.empty((n, top), dtype=torch.float32, device=dev)
     call("b200_moe_route", ptr(h), ptr(router), ptr(bias), ptr(ids), ptr(weights), n, width, experts, top, tag(h.dtype), stream_ptr())
-    tile = tile_rows()
+    tile = TC_TILE_ROWS if wide_tiles else tile_rows()
     max_tiles = min(-(-n * top // tile) + experts, n * top)       # a tile holds one expert's rows only
     pair_row = torch.empty(n * top, dtype=torch.int32, device=dev)
     sorted_token = torch.empty(max_tiles * tile, dtype=torch.int32, device=dev)
     tile_group = torch.empty(max_tiles, dtype=torch.int32, device=dev)
-    call("b200_moe_plan", ptr(ids), n * top, top, experts, ptr(sorted_token), ptr(pair_row), ptr(tile_group), max_tiles, stream_ptr())
-    return Routing(ids, weights, pair_row, sorted_token, tile_group, top)
+    call("b200_moe_plan", ptr(ids), n * top, top, experts, ptr(sorted_token), ptr(pair_row), ptr(tile_group), max_tiles, tile, stream_ptr())
+    return Routing(ids, weights, pair_row, sorted_token, tile_group, top, tile)
+
+
+def wide_tiles_pay(n: int, top: int, dtype: torch.dtype, *widths: int) -> bool:
+    """Whether the experts' products of ``n`` tokens go to the tcgen05 kernel."""
+
+    return (EXPERTS_BACKEND == "tcgen05" and dtype == torch.bfloat16 and n * top >= TC_MIN_PAIRS and all(w % 8 == 0 for w in widths))
+
+
+def gather_sorted(x: torch.Tensor, routing: Routing) -> torch.Tensor:
+    """``x``'s rows in the sorted order, zeros in the padding (bfloat16, a width in steps of eight)."""
+
+    require(x, "x", dtype=torch.bfloat16, dims=2)
+    out = torch.empty((routing.rows, x.shape[1]), dtype=x.dtype, device=x.device)
+    call("b200_gather_rows_bf16", ptr(x), ptr(routing.sorted_token), ptr(out), routing.rows, x.shape[1], stream_ptr())
+    return out
 
 
 def expert_linear(a: torch.Tensor, weight: torch.Tensor, routing: Routing, *, gather: bool, act: str | None = None,
                   out_dtype: torch.dtype | None = None) -> torch.Tensor:
     """``out[row] = act(W[expert of row] @ a[source of row])`` for every sorted row.  ``weight`` ``[experts, n_out, k]``.  With
     ``gather`` the source is the row's token (``a`` is ``[N, k]``); otherwise ``a`` is already in sorted order (``[rows, k]``).
-    ``act``: ``"relu2"`` (the square of relu) or ``None``.  Rows of the padding are not written."""
+    ``act``: ``"relu2"`` (the square of relu) or ``None``.  Rows of the padding are not written, or hold zeros.
+
+    A routing made with tiles of 128 rows (bfloat16, widths in steps of eight) goes to the tcgen05 kernel, which fetches its
+    operands by TMA: the gathered rows are then laid out first (one more launch).  Everything else runs on mma.sync tiles
+    (bfloat16) or FFMA (float32) with the gather inside the kernel."""
 
     require(a, "a", dims=2)
     require(weight, "weight", dtype=a.dtype, dims=3)
@@ -107,9 +135,19 @@ def expert_linear(a: torch.Tensor, weight: torch.Tensor, routing: Routing, *, ga
     if a.shape[1] != k or (not gather and a.shape[0] != routing.rows):
         raise KernelError(f"expert_linear: a {tuple(a.shape)} does not fit the weight {tuple(weight.shape)} and {routing.rows} sorted rows")
     out = torch.empty((routing.rows, n_out), dtype=out_dtype or a.dtype, device=a.device)
+    code = {None: 0, "relu2": 1}[act]
+    if (routing.tile_rows == TC_TILE_ROWS and a.dtype == torch.bfloat16 and k % 8 == 0 and weight.is_contiguous()
+            and EXPERTS_BACKEND == "tcgen05"):
+        from . import gemm_bf16  # noqa: F401  (registers the library)
+
+        rows = gather_sorted(a, routing) if gather else a
+        call("b200_gemm_tcgen05_grouped", ptr(rows), ptr(weight), ptr(out), routing.rows, n_out, k, out.stride(0),
+             1 if out.dtype == torch.float32 else 0, code, ptr(routing.tile_group), experts, 256 if n_out >= 256 else 128, stream_ptr(),
+             launches=2 if gather else 1)
+        return out
     call("b200_gemm_grouped", ptr(a), a.stride(0), 0, ptr(routing.sorted_token), 1 if gather else 0, ptr(weight), weight.stride(1),
-         weight.stride(0), 0, None, 0, ptr(out), out.stride(0), 0, ptr(routing.tile_group), routing.rows, n_out, k, 1,
-         {None: 0, "relu2": 1}[act], tag(a.dtype), tag(out.dtype), stream_ptr())
+         weight.stride(0), 0, None, 0, ptr(out), out.stride(0), 0, ptr(routing.tile_group), routing.tile_rows, routing.rows, n_out, k, 1,
+         code, tag(a.dtype), tag(out.dtype), stream_ptr())
     return out
 
 

@@ -155,7 +155,8 @@ def gated_recurrence(gates: torch.Tensor, u: torch.Tensor, proj: torch.Tensor, *
                      decay_scale: float, state: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor, block_width: int) -> torch.Tensor:
     """Per request (entry ``e`` owns rows ``q_start[e] .. q_start[e+1]-1`` and the state row ``slots[e]``) and channel, token after
     token: ``r, i = sigmoid(gates)``, ``log a = -decay_scale r softplus(lam)``, ``S <- a S + sqrt(1 - a^2) i u``; the result is
-    ``S * gelu_tanh(proj[:, y_offset + c])`` in ``u``'s type.  ``gates`` float32 ``[N, blocks, 2 * block_width]`` (r logits, then i
+    ``S * gelu_tanh(proj[:, y_offset + c])`` in ``u``'s type.  Two launches: everything that does not depend on the state for all
+    (token, channel) at once, then the chain of multiply-adds per channel.  ``gates`` float32 ``[N, blocks, 2 * block_width]`` (r logits, then i
     logits, per block); ``state`` ``[slots, width]`` float32, updated in place."""
 
     require(u, "u", dims=2)
@@ -169,6 +170,8 @@ def gated_recurrence(gates: torch.Tensor, u: torch.Tensor, proj: torch.Tensor, *
     entries = q_start.shape[0] - 1
     require(slots, "slots", dtype=torch.int32, shape=(entries,))
     out = torch.empty_like(u)
+    scratch = torch.empty((2, n, width), dtype=torch.float32, device=u.device)      # a and b of every (token, channel)
     call("b200_gated_recurrence", ptr(gates), ptr(u), ptr(proj), proj.shape[1], y_offset, ptr(lam), float(decay_scale), ptr(state),
-         ptr(q_start), ptr(slots), ptr(out), entries, width, block_width, tag(u.dtype), stream_ptr())
+         ptr(q_start), ptr(slots), ptr(out), ptr(scratch[0]), ptr(scratch[1]), n, entries, width, block_width, tag(u.dtype),
+         stream_ptr(), launches=2)
     return out

@@ -110,18 +110,19 @@ _LIBRARIES = {
             "b200_conv_taps": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                c_int, c_int, c_int, c_void_p],
             "b200_gated_recurrence": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
-                                      c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+                                      c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
         },
     ),
     "b200_gemm_grouped": (
         ("gemm_grouped.cu",),
         {
             "b200_gemm_grouped": [c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_void_p, c_longlong, c_longlong, c_int,
-                                  c_void_p, c_longlong, c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_int, c_int, c_int,
+                                  c_void_p, c_longlong, c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                   c_int, c_int, c_int, c_void_p],
             "b200_moe_route": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
             "b200_moe_tile_rows": [],
-            "b200_moe_plan": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+            "b200_moe_plan": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+            "b200_gather_rows_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
             "b200_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         },
     ),

@@ -50,7 +50,8 @@ class RoutedExperts(FeedForward):
         self.down = torch.stack([runtime.place_matrix(tensors[f"e{e}.down"]) for e in range(self.experts)])
 
     def forward(self, x: torch.Tensor, ctx: Any) -> torch.Tensor:
-        routing = G.route(x, self.router, self.router_b, top=self.top)
+        wide = G.wide_tiles_pay(x.shape[0], self.top, x.dtype, self.hidden_size, self.intermediate_size)
+        routing = G.route(x, self.router, self.router_b, top=self.top, wide_tiles=wide)
         hidden = G.expert_linear(x, self.up, routing, gather=True, act=self.act)
         rows = G.expert_linear(hidden, self.down, routing, gather=False, out_dtype=torch.float32)
         return G.combine(rows, routing)

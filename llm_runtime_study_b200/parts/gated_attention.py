@@ -8,6 +8,7 @@ from typing import Any, Mapping
 
 import torch
 
+from ..ops import attention_latent
 from ..ops import functional as F
 from ..ops import grouped as G
 from ..ops import mixer_steps as M
@@ -169,9 +170,8 @@ class LatentAttention(Mixer):
         if self.rot_dim:
             M.rope_slice(q, absorbed, heads=H, src_head=q_head, src_offset=self.head_dim, dst_head=row, dst_offset=self.kv_rank,
                          rot=self.rot_dim, rot_dims=rot_dims, inv_freq=inv_freq, positions=ctx.positions)
-        mixed = F.paged_attention_simt_latent(absorbed.view(n, H, row), pool, value_dim=self.kv_rank, positions=ctx.positions,
-                                              token_entry=ctx.token_entry, block_table=table, scale=self.scale,
-                                              window=self.window or 0)
+        mixed = attention_latent.latent_attention(absorbed.view(n, H, row), pool, ctx, table, value_dim=self.kv_rank, scale=self.scale,
+                                                  window=self.window or 0)
         out = G.batched_linear(mixed.view(n, H * self.kv_rank), self.uv, batch=H, k=self.kv_rank, n_out=self.value_dim,
                                a_batch_stride=self.kv_rank)
         gate_offset = self.q_rank + (self.kv_rank + self.rot_dim if own else 0)

@@ -306,7 +306,24 @@ ROPULIX_B = {
          "mlp": {"kind": "moe", "expert": {"ff": 16}, "router": {"experts": 6, "top": 3}}},
     ],
 }
-ROPULIX = {"A": (ROPULIX_A, 21, 4), "B": (ROPULIX_B, 22, 16)}   # config, seed, page size
+# C: sizes in steps of 16 throughout, which is what the tensor-core kernels of the bfloat16 run type take: latent rows of
+# 32 + 16 columns shared by two layers with windows of 24 and 50, heads of 32 and 64, experts of 64 hidden units.
+ROPULIX_C = {
+    "architecture": "Ropulix", "vocab": 151, "width": 128, "norm": {"eps": 1e-6},
+    "layers": [
+        {"type": "attention", "mixer": {"heads": 4, "kv_heads": 2, "dim": 32, "vdim": 32, "mask": {"size": 20}, "scale": 0.2},
+         "mlp": {"kind": "moe", "expert": {"ff": 64}, "router": {"experts": 6, "top": 2}}},
+        {"type": "latent_attention", "mixer": {"heads": 5, "dim": 16, "rot_dim": 16, "vdim": 32, "kv_rank": 32, "q_rank": 48,
+                                               "mask": {"size": 50}, "rot": {"base": 5000.0, "dims": 16}, "scale": 0.25},
+         "mlp": {"kind": "moe", "expert": {"ff": 64}, "router": {"experts": 6, "top": 2}}},
+        {"type": "rglru", "mixer": {"width": 128, "blocks": 2, "conv": 3},
+         "mlp": {"kind": "moe", "expert": {"ff": 64}, "router": {"experts": 6, "top": 2}}},
+        {"type": "latent_attention", "mixer": {"heads": 3, "dim": 64, "rot_dim": 16, "vdim": 16, "kv_rank": 32, "q_rank": 32, "kv_from": 1,
+                                               "mask": {"size": 24}, "rot": {"base": 5000.0, "dims": 16}, "scale": 0.12},
+         "mlp": {"kind": "moe", "expert": {"ff": 64}, "router": {"experts": 6, "top": 2}}},
+    ],
+}
+ROPULIX = {"A": (ROPULIX_A, 21, 4), "B": (ROPULIX_B, 22, 16), "C": (ROPULIX_C, 23, 16)}   # config, seed, page size
 
 
 def make_ropulix_dir(path: Path, config: dict, seed: int, *, torch_dtype: str = "float32", gain: float = 6.0):

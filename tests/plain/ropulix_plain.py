@@ -172,10 +172,15 @@ def rglru_mixer(h, w: Mapping[str, torch.Tensor], m: Mapping, store=keep) -> tor
 
 
 # ---------------------------------------------------------------- feed-forward
-def moe(h, w: Mapping[str, torch.Tensor], m: Mapping, store=keep) -> torch.Tensor:
+def moe(h, w: Mapping[str, torch.Tensor], m: Mapping, store=keep, margins=None) -> torch.Tensor:
+    """``margins`` (a list) receives, per token, how far the last chosen logit lies above the first one left out."""
+
     experts, top = m["router"]["experts"], m["router"]["top"]
     z = h @ w["router"].T + w["router.b"]
     chosen = torch.topk(z, top, dim=-1)
+    if margins is not None and top < experts:
+        ranked = torch.sort(z, dim=-1, descending=True).values
+        margins.append(ranked[:, top - 1] - ranked[:, top])
     weights = torch.softmax(chosen.values, dim=-1)
     out = torch.zeros(h.shape[0], w["e0.down"].shape[0], dtype=h.dtype)
     for e in range(experts):
@@ -191,8 +196,10 @@ def sub(weights: Mapping[str, torch.Tensor], prefix: str, dtype) -> dict:
     return {k[len(prefix):]: (v.to(dtype) if v.is_floating_point() else v) for k, v in weights.items() if k.startswith(prefix)}
 
 
-def forward(config: Mapping, weights: Mapping[str, torch.Tensor], tokens, dtype=torch.float64, store=keep, layers_out=None):
-    """Logits ``[T, vocab]`` of one sequence.  ``layers_out`` (a list) receives the residual rows after every layer."""
+def forward(config: Mapping, weights: Mapping[str, torch.Tensor], tokens, dtype=torch.float64, store=keep, layers_out=None,
+            margins=None):
+    """Logits ``[T, vocab]`` of one sequence.  ``layers_out`` (a list) receives the residual rows after every layer,
+    ``margins`` (a list) every router's margins per token (see ``moe``)."""
 
     eps = config["norm"]["eps"]
     tokens = torch.as_tensor(tokens, dtype=torch.long)
@@ -219,7 +226,7 @@ def forward(config: Mapping, weights: Mapping[str, torch.Tensor], tokens, dtype=
             raise ValueError(layer["type"])
         x = x + rms_norm(out, weights[f"l{i}.norm1"].to(dtype), eps)
         if layer.get("mlp"):
-            out = moe(store(x), sub(weights, f"l{i}.mlp.", dtype), layer["mlp"], store)
+            out = moe(store(x), sub(weights, f"l{i}.mlp.", dtype), layer["mlp"], store, margins)
             x = x + rms_norm(out, weights[f"l{i}.norm2"].to(dtype), eps)
         if layers_out is not None:
             layers_out.append(x.clone())

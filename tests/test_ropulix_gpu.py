@@ -18,11 +18,12 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 # a row of logits against the plain model in 64-bit, as fractions of the row's root mean square: (rms, largest).
 # float32 is the sharp comparison.  bfloat16: the plain model rounds its activations where the engine stores them; a
-# router's close call or a rounding that falls the other way moves single rows by several per cent, so a request passes
-# when at most a tenth of its rows (or one) is beyond BF16_USUAL and none beyond BF16_WORST.  A wrong state, slot or page
-# moves every row after it; the kernels alone are compared sharply above.
+# rounding that falls the other way moves single rows by several per cent, so a request passes when at most a tenth of its
+# rows (or one) is beyond BF16_USUAL and none beyond BF16_WORST.  A row at which some router's last chosen logit lies within
+# CLOSE_CALL of the first one left out is not judged: there the two models may rightly send the token to different experts.
+# A wrong state, slot or page moves every row after it; the kernels alone are compared sharply above.
 TOL = {"float32": (3e-5, 2e-4)}
-BF16_USUAL, BF16_WORST = 6e-2, 5e-1
+BF16_USUAL, BF16_WORST, CLOSE_CALL = 6e-2, 5e-1, 0.15
 
 
 def dev(t):
@@ -151,6 +152,81 @@ def test_a_key_at_the_windows_edge_and_a_far_key(dtype, page, window, marked):
     assert (out - want).abs().max() <= (2e-5 if dtype == torch.float32 else 3e-2)
 
 
+def _latent_ctx(lengths, q_lens):
+    """What the kernel chooser reads of a step's context: every sequence of ``lengths`` brings its last ``q_lens`` tokens."""
+
+    from types import SimpleNamespace
+
+    positions = torch.cat([torch.arange(m - k, m) for m, k in zip(lengths, q_lens)]).int()
+    entry = torch.cat([torch.full((k,), i) for i, k in enumerate(q_lens)]).int()
+    return SimpleNamespace(positions=dev(positions), token_entry=dev(entry), all_decode=max(q_lens) == 1, num_entries=len(lengths),
+                           q_lens=list(q_lens), kv_lens=list(lengths)), positions, entry
+
+
+@pytest.mark.parametrize("heads,rank,rot,page,window", [(3, 32, 16, 4, 9), (6, 64, 16, 16, 40), (16, 128, 64, 16, 0), (70, 48, 0, 8, 33),
+                                                        (5, 512, 64, 16, 100)])
+@pytest.mark.parametrize("q_lens", [[150, 41], [1, 1], [2, 37]])
+def test_tensor_core_latent_attention(heads, rank, rot, page, window, q_lens):
+    """The mma.sync kernel for prompt portions behind cached tokens and for single tokens, several tokens and head groups a
+    tile, against the plain attention of each sequence."""
+
+    from llm_runtime_study_b200.ops import attention_latent
+
+    torch.manual_seed(rank + heads)
+    lengths, d = [150, 41], rank + rot
+    assert attention_latent.supported(rank, rot)
+    table, pages = _pages(rank, page, lengths)
+    rows = [0.5 * torch.randn(m, d).bfloat16() for m in lengths]
+    pool = torch.zeros(pages, page, d, dtype=torch.bfloat16)
+    for e, m in enumerate(lengths):
+        for t in range(m):
+            pool[table[e, t // page], t % page] = rows[e][t]
+    ctx, positions, entry = _latent_ctx(lengths, q_lens)
+    q = (0.5 * torch.randn(sum(q_lens), heads, d)).bfloat16()
+    got = attention_latent.latent_attention(dev(q), dev(pool), ctx, dev(table), value_dim=rank, scale=0.3, window=window).cpu().double()
+    at = 0
+    for e, (m, k) in enumerate(zip(lengths, q_lens)):
+        full_q = torch.zeros(m, heads, d, dtype=torch.float64)
+        full_q[m - k:] = q[at:at + k].double()
+        keys = rows[e].double()[:, None, :]
+        want = plain.softmax_attention(full_q, keys, keys[:, :, :rank], scale=0.3, window=window or None)[m - k:]
+        assert (got[at:at + k] - want).abs().max() <= 2e-2 * max(1.0, float(want.abs().max())), (e, float((got[at:at + k] - want).abs().max()))
+        at += k
+
+
+@pytest.mark.parametrize("page,window,marked", [(16, 40, 15), (16, 40, 16), (8, 9, 63), (4, 5, 100), (16, 0, 3), (16, 64, 31), (16, 33, 32)])
+@pytest.mark.parametrize("new", [700, 1])
+def test_tensor_core_latent_attention_at_the_windows_edge(page, window, marked, new):
+    """One key stands out, in a whole prompt and for single tokens fed behind cached ones: the last position that sees it gives
+    nearly its value, the next one does not; without a window a key hundreds of positions back is found."""
+
+    from llm_runtime_study_b200.ops import attention_latent
+
+    heads, rank, rot, length = 2, 16, 16, 700
+    q, rows, pool, table = _latent_case(torch.bfloat16, heads, rank, rot, page, length, window, marked=marked, seed=marked)
+    last_seen = marked + window - 1 if window else length - 1
+    k = rows.double()[:, None, :]
+    want = plain.softmax_attention(q.double(), k, k[:, :, :rank], scale=1.0, window=window or None)
+    value = rows[marked, :rank].double()
+    if new == length:
+        ctx, _, _ = _latent_ctx([length], [length])
+        out = attention_latent.latent_attention(dev(q), dev(pool), ctx, dev(table), value_dim=rank, scale=1.0, window=window).cpu().double()
+        probes = {p: out[p] for p in (marked, last_seen - 1, last_seen, min(last_seen + 1, length - 1), min(last_seen + 2, length - 1))}
+        assert (out - want).abs().max() <= 3e-2
+    else:
+        probes = {}
+        for p in (marked, last_seen - 1, last_seen, min(last_seen + 1, length - 1), min(last_seen + 2, length - 1)):
+            ctx, _, _ = _latent_ctx([p + 1], [1])
+            probes[p] = attention_latent.latent_attention(dev(q[p:p + 1].contiguous()), dev(pool), ctx, dev(table), value_dim=rank, scale=1.0,
+                                                          window=window).cpu().double()[0]
+            assert (probes[p] - want[p]).abs().max() <= 3e-2
+    for p, row in probes.items():
+        if p <= last_seen:
+            assert (row - value).abs().max() < 0.05, p
+        else:
+            assert (row[:, 1] - 4.0).abs().min() > 2.0, p
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("q_rank,kv_rank,rot,rot_dims,page", [(48, 40, 8, 8, 4), (12, 24, 16, 16, 16), (20, 8, 12, 8, 8)])
 def test_latent_rows_and_rotations(dtype, q_rank, kv_rank, rot, rot_dims, page):
@@ -272,15 +348,20 @@ def test_convolution_gates_and_recurrence_across_cuts(dtype, taps, blocks, cuts)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("n,width,ff,experts,top", [(70, 48, 40, 5, 2), (3, 64, 24, 3, 3), (200, 32, 16, 7, 1), (1, 40, 72, 12, 3)])
+@pytest.mark.parametrize("n,width,ff,experts,top", [(70, 48, 40, 5, 2), (3, 64, 24, 3, 3), (200, 32, 16, 7, 1), (1, 40, 72, 12, 3),
+                                                    (700, 64, 48, 5, 2), (300, 128, 320, 3, 2)])
 def test_router_and_experts_against_plain(dtype, n, width, ff, experts, top):
+    """The last two cases bring enough rows for the tiles of 128 rows an expert that the tcgen05 kernel takes (bfloat16)."""
+
     from llm_runtime_study_b200.ops import grouped as G
 
     torch.manual_seed(n)
     h = torch.randn(n, width).to(dtype)
     router, rb = torch.randn(experts, width), torch.randn(experts)
     up, down = (0.3 * torch.randn(experts, ff, width)).to(dtype), (0.3 * torch.randn(experts, width, ff)).to(dtype)
-    routing = G.route(dev(h), dev(router), dev(rb), top=top)
+    wide = G.wide_tiles_pay(n, top, dtype, width, ff)
+    assert wide == (dtype == torch.bfloat16 and n * top >= 512)
+    routing = G.route(dev(h), dev(router), dev(rb), top=top, wide_tiles=wide)
     z = h.double() @ router.double().T + rb.double()
     chosen = torch.topk(z, top, dim=-1)
     assert torch.equal(routing.ids.cpu().long(), chosen.indices)
@@ -296,7 +377,7 @@ def test_router_and_experts_against_plain(dtype, n, width, ff, experts, top):
     tol = 2e-5 if dtype == torch.float32 else 2e-2
     assert (got - want).abs().max() <= tol * max(1.0, float(want.abs().max()))
     # the sorted order: every pair has a row of its expert's tiles, padding rows belong to nobody
-    tile = G.tile_rows()
+    tile = routing.tile_rows
     sorted_token, pair_row, tile_group = routing.sorted_token.cpu(), routing.pair_row.cpu(), routing.tile_group.cpu()
     assert sorted(pair_row.tolist()) == sorted((sorted_token >= 0).nonzero().flatten().tolist())
     for p, row in enumerate(pair_row.tolist()):
@@ -335,7 +416,7 @@ def test_batched_products_with_strides():
 
 
 # ------------------------------------------------------------------------------------------- whole models
-LENGTHS = {"A": [1, 2, 5, 23, 64, 65, 131], "B": [3, 17, 48, 70, 1, 129]}
+LENGTHS = {"A": [1, 2, 5, 23, 64, 65, 131], "B": [3, 17, 48, 70, 1, 129], "C": [140, 2, 37, 66, 300]}
 
 
 def _requests(name):
@@ -344,7 +425,7 @@ def _requests(name):
     return {f"r{i}": helpers.random_tokens(rng, config["vocab"], n) for i, n in enumerate(LENGTHS[name])}
 
 
-@pytest.fixture(scope="module", params=[(n, d) for n in ("A", "B") for d in ("float32", "bfloat16")], ids=lambda p: f"{p[0]}-{p[1]}")
+@pytest.fixture(scope="module", params=[(n, d) for n in ("A", "B") for d in ("float32", "bfloat16")] + [("C", "bfloat16")], ids=lambda p: f"{p[0]}-{p[1]}")
 def setup(request, tmp_path_factory):
     from llm_runtime_study_b200.engine.runtime import load
 
@@ -353,10 +434,14 @@ def setup(request, tmp_path_factory):
     path, weights = helpers.make_ropulix_dir(tmp_path_factory.mktemp(f"ropulix{name}{dtype}"), config, seed, torch_dtype=dtype)
     requests = _requests(name)
     store = plain.round_bfloat16 if dtype == "bfloat16" else plain.keep
-    expected = {rid: plain.forward(config, weights, tokens, store=store) for rid, tokens in requests.items()}
+    expected, clear = {}, {}
+    for rid, tokens in requests.items():
+        margins = []
+        expected[rid] = plain.forward(config, weights, tokens, store=store, margins=margins)
+        clear[rid] = torch.stack(margins).min(dim=0).values > CLOSE_CALL if margins else torch.ones(len(tokens), dtype=torch.bool)
     loaded = load(path, device=DEV, dtype=dtype, strict_dtype=False)
     return dict(name=name, dtype=dtype, config=config, page=page, path=path, requests=requests, plain=expected, loaded=loaded,
-                weights=weights)
+                weights=weights, clear=clear)
 
 
 def _replay(setup, steps, *, max_requests=4, max_tokens=None):
@@ -382,7 +467,11 @@ def _compare(setup, got, requests=None):
         if setup["dtype"] == "bfloat16":
             want = setup["plain"][rid]
             err = (rows - want).pow(2).mean(dim=1).sqrt() / want.pow(2).mean(dim=1).sqrt()
-            assert torch.isfinite(err).all() and float(err.max()) <= BF16_WORST, (rid, int(err.argmax()), float(err.max()))
+            assert torch.isfinite(err).all()
+            clear = setup["clear"][rid]
+            assert int(clear.sum()) >= len(tokens) // 2, "the weights make too many close calls for this test to judge anything"
+            err = torch.where(clear, err, torch.zeros_like(err))
+            assert float(err.max()) <= BF16_WORST, (rid, int(err.argmax()), float(err.max()))
             over = int((err > BF16_USUAL).sum())
             assert over <= max(1, len(tokens) // 10), f"request {rid}: {over} of {len(tokens)} rows beyond {BF16_USUAL}: {err}"
             continue
@@ -416,7 +505,7 @@ def test_mixed_batches_with_slots_and_pages_used_again(setup):
 def test_every_token_decoded_alone(setup):
     """A sequence fed one token a step from its first token: the first tokens, long decoding."""
 
-    requests = {rid: tokens for rid, tokens in setup["requests"].items() if len(tokens) in (23, 131, 70)}
+    requests = {rid: tokens for rid, tokens in setup["requests"].items() if len(tokens) in (23, 131, 70, 66)}
     _compare(setup, _replay(setup, helpers.trace_decode_tail(requests, tail=10_000)), requests)
 
 
@@ -433,7 +522,7 @@ def test_a_cut_changes_no_bit_in_float32(setup):
 def test_a_reused_slot_starts_from_zero(setup):
     """One slot: the second request takes the first one's state rows, convolution inputs and pages."""
 
-    requests = {rid: tokens for rid, tokens in setup["requests"].items() if len(tokens) in (23, 17, 48, 65)}
+    requests = {rid: tokens for rid, tokens in setup["requests"].items() if len(tokens) in (23, 17, 48, 65, 37, 66)}
     _compare(setup, _replay(setup, helpers.trace_chunked(requests, random.Random(3), sizes=(7, 16)), max_requests=1), requests)
 
 

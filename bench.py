@@ -876,7 +876,7 @@ def _ropulix_kernels(peak, timed) -> dict:
         positions = torch.cat([torch.arange(m - k, m) for m, k in zip(lengths, q_lens)]).int().to(dev)
         entry = torch.cat([torch.full((k,), i) for i, k in enumerate(q_lens)]).int().to(dev)
         ctx = SimpleNamespace(positions=positions, token_entry=entry, all_decode=max(q_lens) == 1, num_entries=seqs, q_lens=q_lens,
-                              kv_lens=lengths)
+                              kv_lens=lengths, max_kv_len=max(lengths))
         t = timed(lambda: attention_latent.latent_attention(q, pool, ctx, table, value_dim=rank, scale=0.07, window=ROPULIX_WINDOW), 3)
         t_simt = cold(lambda: F.paged_attention_simt_latent(q, pool, value_dim=rank, positions=positions, token_entry=entry,
                                                             block_table=table, scale=0.07, window=ROPULIX_WINDOW), 1)

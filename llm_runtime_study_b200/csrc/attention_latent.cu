@@ -39,6 +39,11 @@ struct LatentParams {
   const int* tile_count;
   int table_stride, page_size, heads, group_heads, tokens_per_tile, window;
   float scale_log2;
+  // a tile's keys cut into `splits` parts (single tokens only): CTA z takes its share of the key tiles and leaves
+  // (maximum, sum) and the unnormalised output of row token * heads + head in scratch memory for the merge kernel
+  int splits;
+  float* part_o;    // [rows][splits][DV]
+  float* part_ml;   // [rows][splits][2]
 };
 
 __device__ __forceinline__ void load_key_tile(bf16* ks, const LatentParams& p, const int* table, int t0, int lo, int hi) {
@@ -98,8 +103,14 @@ latent_attention_kernel(const LatentParams p) {
       cp_async_16(qs + r * LDS + ch * 8, src, valid ? 16 : 0);
     }
   }
-  const int t_begin = (lo / BN) * BN;
-  const int tiles = hi >= t_begin ? (hi - t_begin) / BN + 1 : 0;
+  int t_begin = (lo / BN) * BN;
+  int tiles = hi >= t_begin ? (hi - t_begin) / BN + 1 : 0;
+  if (p.splits > 1) {          // this CTA's share of the key tiles
+    const int per = (tiles + p.splits - 1) / p.splits;
+    const int first_tile = min(tiles, static_cast<int>(blockIdx.z) * per);
+    tiles = min(tiles - first_tile, per);
+    t_begin += first_tile * BN;
+  }
   if (tiles > 0) load_key_tile(ks, p, table, t_begin, lo, hi);
   cp_async_commit();
 
@@ -195,6 +206,21 @@ latent_attention_kernel(const LatentParams p) {
     __syncthreads();
   }
   cp_async_wait<0>();
+  if (p.splits > 1) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      if (row_token[i] < 0 || row_head[i] >= p.heads) continue;
+      const size_t slot = (static_cast<size_t>(row_token[i]) * p.heads + row_head[i]) * p.splits + blockIdx.z;
+      if (half == 0 && (lane & 3) == 0) {
+        p.part_ml[slot * 2] = m[i];
+        p.part_ml[slot * 2 + 1] = l[i];
+      }
+      float* dst = p.part_o + slot * DV + half * DVH + (lane & 3) * 2;
+#pragma unroll
+      for (int j = 0; j < OTILES; ++j) *reinterpret_cast<float2*>(dst + j * 8) = make_float2(o[j][i * 2], o[j][i * 2 + 1]);
+    }
+    return;
+  }
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     if (row_token[i] < 0 || row_head[i] >= p.heads || (rg * 16 + (lane >> 2) + i * 8) / hg >= p.tokens_per_tile) continue;
@@ -206,6 +232,30 @@ latent_attention_kernel(const LatentParams p) {
   }
 }
 
+// out[row] = sum_z 2^(m_z - M) o_z / sum_z 2^(m_z - M) l_z over the parts of a row's keys, M the largest maximum.
+__global__ void __launch_bounds__(128)
+latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out, int splits) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t row = blockIdx.x;
+  float top = -INFINITY;
+  for (int z = 0; z < splits; ++z) top = fmaxf(top, part_ml[(row * splits + z) * 2]);
+  float total = 0.f;
+  for (int z = 0; z < splits; ++z) {
+    const float mz = part_ml[(row * splits + z) * 2];
+    total += mz == -INFINITY ? 0.f : exp2f(mz - top) * part_ml[(row * splits + z) * 2 + 1];
+  }
+  const float inv = total > 0.f ? 1.f / total : 0.f;
+  for (int c = threadIdx.x; c < DV; c += blockDim.x) {
+    float acc = 0.f;
+    for (int z = 0; z < splits; ++z) {
+      const float mz = part_ml[(row * splits + z) * 2];
+      if (mz != -INFINITY) acc = fmaf(exp2f(mz - top), part_o[(row * splits + z) * DV + c], acc);
+    }
+    out[row * DV + c] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
 DeviceOnce latent_once;
 
 }  // namespace b200
@@ -214,13 +264,17 @@ extern "C" int b200_attention_latent_rank() { return b200::DV; }
 extern "C" int b200_attention_latent_rot() { return LATENT_ROT; }
 
 // q [n, heads, DK], pool [pages, page_size, DK], out [n, heads, DV]; tiles: (entry, first row, rows) of consecutive
-// tokens of one entry, at most tokens_per_tile = max(1, 64 / heads) each.
+// tokens of one entry, at most tokens_per_tile = max(1, 64 / heads) each.  splits > 1 (every tile is token t alone, tile t):
+// the keys of a token are cut into that many parts, merged by a second launch; scratch holds splits * (DV + 2) floats a row.
 extern "C" int b200_attention_latent_bf16(const void* q, const void* pool, void* out, const int* positions, const int* block_table,
                                           int table_stride, int page_size, int heads, float scale, int window, const int* tile_entry,
-                                          const int* tile_start, const int* tile_count, int num_tiles, cudaStream_t stream) {
+                                          const int* tile_start, const int* tile_count, int num_tiles, int splits, float* scratch,
+                                          long scratch_floats, cudaStream_t stream) {
   using namespace b200;
   if (num_tiles <= 0) return 0;
-  if (heads <= 0 || page_size <= 0 || window < 0) return B200_ERR_BAD_SIZE;
+  if (heads <= 0 || page_size <= 0 || window < 0 || splits < 1 || splits > 64) return B200_ERR_BAD_SIZE;
+  // parts only for single tokens (one tile a token): the scratch rows are token * heads + head
+  if (splits > 1 && (scratch == nullptr || scratch_floats < static_cast<long>(num_tiles) * heads * splits * (DV + 2))) return 10004;
   const int status = configure_once(latent_once, latent_attention_kernel, kSmemBytes);
   if (status != 0) return status;
   LatentParams p{};
@@ -239,8 +293,15 @@ extern "C" int b200_attention_latent_bf16(const void* q, const void* pool, void*
   p.tokens_per_tile = BM / p.group_heads;
   p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
-  dim3 grid(num_tiles, (heads + p.group_heads - 1) / p.group_heads);
+  p.splits = splits;
+  if (splits > 1) {
+    p.tokens_per_tile = 1;
+    p.part_o = scratch;
+    p.part_ml = scratch + static_cast<size_t>(num_tiles) * heads * splits * DV;
+  }
+  dim3 grid(num_tiles, (heads + p.group_heads - 1) / p.group_heads, splits);
   if (grid.y > 65535) return B200_ERR_TOO_LARGE;
   launch(latent_attention_kernel, grid, dim3(NT), kSmemBytes, stream, p);
+  if (splits > 1) launch(latent_merge_kernel, dim3(num_tiles * heads), dim3(128), 0, stream, p.part_o, p.part_ml, p.out, splits);
   return launch_status();
 }

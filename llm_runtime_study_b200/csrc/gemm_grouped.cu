@@ -104,11 +104,12 @@ grouped_gemm_kernel(const GroupedArgs g) {
 }
 
 // ----------------------------------------------------------------------------- bfloat16 on the tensor cores
-// The same tile space (BM rows of one group or batch entry) with BN = 128 columns and BK = 32 per stage.  Eight warps,
+// The same tile space (BM rows of one group or batch entry) with BN = 128 columns and BK = 64 per stage, four stages
+// (110 KB in flight per CTA: what a few rows against a large weight need to stream it).  Eight warps,
 // two along the rows and four along the columns, each 32 x 32 outputs.  Every 16-byte chunk of A and W must start on a
 // 16-byte boundary: base pointers, row strides and batch strides are multiples of 8 elements (the launcher checks).
-constexpr int TBN = 128, TBK = 32, TPAD = 8, TSTAGES = 3;
-constexpr int TLD = TBK + TPAD;                         // 40 halves = 80 bytes a row: ldmatrix reads hit every bank once
+constexpr int TBN = 128, TBK = 64, TPAD = 8, TSTAGES = 4;
+constexpr int TLD = TBK + TPAD;                         // 72 halves = 144 bytes a row: ldmatrix reads hit every bank once
 constexpr int TSTAGE_HALVES = (BM + TBN) * TLD;
 
 template <typename TOut, int ACT>
@@ -142,22 +143,24 @@ grouped_gemm_mma_kernel(const GroupedArgs g) {
     src_row[tid] = r;
   }
   __syncthreads();
-  // chunks of 8 halves: A has BM x 4 of them (one a thread), W has TBN x 4 (two a thread)
-  const int a_row = tid >> 2, a_chunk = (tid & 3) * 8;
-  const int a_src = src_row[a_row];
+  // chunks of 8 halves: A has BM x 8 of them (two a thread), W has TBN x 8 (four a thread)
   auto stage_load = [&](int stage, int k0) {
     __nv_bfloat16* As = tiles + stage * TSTAGE_HALVES;
     __nv_bfloat16* Ws = As + BM * TLD;
-    {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int c = tid + i * 256;
+      const int a_row = c >> 3, a_chunk = (c & 7) * 8;
+      const int a_src = src_row[a_row];
       const int k = k0 + a_chunk;
       const int bytes = a_src >= 0 ? max(0, min(16, (g.K - k) * 2)) : 0;
       const __nv_bfloat16* src = bytes > 0 ? A + a_src * g.lda + k : A;
       cp_async_16(As + a_row * TLD + a_chunk, src, bytes);
     }
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < 4; ++i) {
       const int c = tid + i * 256;
-      const int row = c >> 2, chunk = (c & 3) * 8;
+      const int row = c >> 3, chunk = (c & 7) * 8;
       const int n = n0 + row, k = k0 + chunk;
       const int bytes = n < g.N ? max(0, min(16, (g.K - k) * 2)) : 0;
       const __nv_bfloat16* src = bytes > 0 ? W + n * g.ldw + k : W;
@@ -222,33 +225,39 @@ template <typename TOut>
 int launch_grouped_mma(const GroupedArgs& g, int batch, int act, cudaStream_t stream) {
   dim3 grid((g.N + TBN - 1) / TBN, (g.M + BM - 1) / BM, batch);
   if (grid.y > 65535 || grid.z > 65535) return B200_ERR_TOO_LARGE;
-  const size_t smem = sizeof(__nv_bfloat16) * TSTAGES * TSTAGE_HALVES;
-  if (act == 1) launch(grouped_gemm_mma_kernel<TOut, 1>, grid, dim3(256), smem, stream, g);
-  else launch(grouped_gemm_mma_kernel<TOut, 0>, grid, dim3(256), smem, stream, g);
+  constexpr size_t smem = sizeof(__nv_bfloat16) * TSTAGES * TSTAGE_HALVES;
+  static DeviceOnce once[2];
+  if (act == 1) {
+    if (int e = configure_once(once[1], grouped_gemm_mma_kernel<TOut, 1>, smem)) return e;
+    launch(grouped_gemm_mma_kernel<TOut, 1>, grid, dim3(256), smem, stream, g);
+  } else {
+    if (int e = configure_once(once[0], grouped_gemm_mma_kernel<TOut, 0>, smem)) return e;
+    launch(grouped_gemm_mma_kernel<TOut, 0>, grid, dim3(256), smem, stream, g);
+  }
   return launch_status();
 }
 
 // ----------------------------------------------------------------------------- router
-// One warp per token: logits z = W_r h + b in float32 (W_r float32 [experts, width], h in the activation type), the `top`
-// largest (the lower index wins a tie), weights = softmax over the chosen logits only.
+// One CTA of 128 threads per token: logits z = W_r h + b in float32 (W_r float32 [experts, width], h in the activation type),
+// the `top` largest (the lower index wins a tie), weights = softmax over the chosen logits only.  Every thread sums its
+// share of the row for eight experts at a time; the shares meet in a warp's shuffle tree and then warp by warp in order, so
+// a token's logits do not depend on the batch around it.
 template <typename T>
 __global__ void __launch_bounds__(128)
 route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ br, int* __restrict__ ids,
-             float* __restrict__ wts, int n, int width, int experts, int top) {
-  extern __shared__ float logits_all[];
+             float* __restrict__ wts, int width, int experts, int top) {
+  extern __shared__ float logits[];          // [experts], then [4][8] partial sums
+  float* part = logits + experts;
   pdl_trigger();
   pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int token = blockIdx.x * (blockDim.x >> 5) + warp;
-  if (token >= n) return;
-  float* logits = logits_all + warp * experts;
+  const int token = blockIdx.x;
   const T* row = h + static_cast<size_t>(token) * width;
-  // eight experts per pass over the row: eight independent sums, each formed in the same order as one alone would be
   for (int e0 = 0; e0 < experts; e0 += 8) {
     float dot[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) dot[j] = 0.f;
-    for (int i = lane; i < width; i += 32) {
+    for (int i = threadIdx.x; i < width; i += 128) {
       const float x = to_float(row[i]);
 #pragma unroll
       for (int j = 0; j < 8; ++j)
@@ -256,11 +265,17 @@ route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float*
     }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const float total_j = warp_sum(dot[j]);
-      if (lane == 0 && e0 + j < experts) logits[e0 + j] = total_j + (br ? br[e0 + j] : 0.f);
+      const float sum = warp_sum(dot[j]);
+      if (lane == 0) part[warp * 8 + j] = sum;
     }
+    __syncthreads();
+    if (threadIdx.x < 8 && e0 + threadIdx.x < experts) {
+      const int j = threadIdx.x;
+      logits[e0 + j] = ((part[j] + part[8 + j]) + part[16 + j]) + part[24 + j] + (br ? br[e0 + j] : 0.f);
+    }
+    __syncthreads();
   }
-  __syncwarp();
+  if (warp != 0) return;
   float first = 0.f, total = 0.f, mine = 0.f;
   int my_id = 0;
   for (int j = 0; j < top; ++j) {
@@ -411,9 +426,9 @@ extern "C" int b200_moe_route(const void* h, const float* wr, const float* br, i
   using namespace b200;
   if (n <= 0) return 0;
   if (width <= 0 || experts <= 0 || top <= 0 || top > experts || top > 32 || experts > 2048) return B200_ERR_BAD_SIZE;
-  const size_t smem = sizeof(float) * 4 * experts;
-  B200_DISPATCH_DTYPE(dtype, T, launch(route_kernel<T>, dim3((n + 3) / 4), dim3(128), smem, stream, static_cast<const T*>(h), wr, br,
-                                       ids, wts, n, width, experts, top));
+  const size_t smem = sizeof(float) * (experts + 32);
+  B200_DISPATCH_DTYPE(dtype, T, launch(route_kernel<T>, dim3(n), dim3(128), smem, stream, static_cast<const T*>(h), wr, br,
+                                       ids, wts, width, experts, top));
   return launch_status();
 }
 

@@ -162,25 +162,65 @@ sigmoid_gate_kernel(const T* __restrict__ x, const T* __restrict__ gate, int gat
 
 // ------------------------------------------------------------- norm on a sublayer's output
 // resid[t] += x[t] * rsqrt(mean(x[t]^2) + eps) * w  (x null: nothing is added); `rounded` (optional) receives the updated
-// rows in the activation type, for the sublayer that reads them next.
+// rows in the activation type, for the sublayer that reads them next.  The sublayer's output row may be given in pieces:
+// with pair_row, row t of x is sum_j pair_w[t, j] * x[pair_row[t, j]] (j ascending; what a router's experts returned for the
+// token), formed here instead of by a launch of its own.  The row is kept in shared memory between the two passes.
 template <typename T>
 __global__ void __launch_bounds__(256)
 norm_accumulate_round_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ resid,
-                             T* __restrict__ rounded, int hidden, float eps) {
+                             T* __restrict__ rounded, int hidden, float eps, const int* __restrict__ pair_row,
+                             const float* __restrict__ pair_w, int top) {
   __shared__ float scratch[32];
+  extern __shared__ __align__(16) float kept[];
   pdl_trigger();
   pdl_wait();
   const size_t base = static_cast<size_t>(blockIdx.x) * hidden;
   float f = 0.f;
   if (x != nullptr) {
     float ss = 0.f;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) ss = fmaf(x[base + i], x[base + i], ss);
+    if (pair_row != nullptr) {
+      for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < top; ++j) {
+          const int p = blockIdx.x * top + j;
+          acc = fmaf(pair_w[p], x[static_cast<size_t>(pair_row[p]) * hidden + i], acc);
+        }
+        kept[i] = acc;
+        ss = fmaf(acc, acc, ss);
+      }
+    } else if ((hidden & 3) == 0) {
+      for (int i = threadIdx.x; i < hidden / 4; i += blockDim.x) {
+        const float4 v = reinterpret_cast<const float4*>(x + base)[i];
+        reinterpret_cast<float4*>(kept)[i] = v;
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+      }
+    } else {
+      for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        kept[i] = x[base + i];
+        ss = fmaf(kept[i], kept[i], ss);
+      }
+    }
     f = rsqrtf(block_sum(ss, scratch) / static_cast<float>(hidden) + eps);
+  }
+  if ((hidden & 3) == 0 && x != nullptr) {
+    for (int i = threadIdx.x; i < hidden / 4; i += blockDim.x) {
+      const float4 v = reinterpret_cast<const float4*>(kept)[i], g = reinterpret_cast<const float4*>(w)[i];
+      float4 r = reinterpret_cast<float4*>(resid + base)[i];
+      r.x += v.x * f * g.x; r.y += v.y * f * g.y; r.z += v.z * f * g.z; r.w += v.w * f * g.w;
+      reinterpret_cast<float4*>(resid + base)[i] = r;
+      if (rounded != nullptr) {
+        rounded[base + 4 * i] = from_float<T>(r.x);
+        rounded[base + 4 * i + 1] = from_float<T>(r.y);
+        rounded[base + 4 * i + 2] = from_float<T>(r.z);
+        rounded[base + 4 * i + 3] = from_float<T>(r.w);
+      }
+    }
+    return;
   }
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     float r = resid[base + i];
     if (x != nullptr) {
-      r += x[base + i] * f * w[i];
+      r += kept[i] * f * w[i];
       resid[base + i] = r;
     }
     if (rounded != nullptr) rounded[base + i] = from_float<T>(r);
@@ -241,11 +281,13 @@ extern "C" int b200_sigmoid_gate(const void* x, const void* gate, int gate_ld, i
 }
 
 extern "C" int b200_norm_accumulate_round(const float* x, const float* w, float* resid, void* rounded, int n, int hidden, float eps,
-                                          int dtype, cudaStream_t stream) {
+                                          const int* pair_row, const float* pair_w, int top, int dtype, cudaStream_t stream) {
   using namespace b200;
   if (n <= 0) return 0;
-  if (hidden <= 0) return B200_ERR_BAD_SIZE;
-  B200_DISPATCH_DTYPE(dtype, T, launch(norm_accumulate_round_kernel<T>, dim3(n), dim3(256), 0, stream, x, w, resid,
-                                       static_cast<T*>(rounded), hidden, eps));
+  if (hidden <= 0 || hidden > 12288 || (pair_row != nullptr && (pair_w == nullptr || top <= 0 || x == nullptr))) return B200_ERR_BAD_SIZE;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(resid)) & 15) return B200_ERR_BAD_SIZE;
+  const size_t smem = x != nullptr ? sizeof(float) * hidden : 0;
+  B200_DISPATCH_DTYPE(dtype, T, launch(norm_accumulate_round_kernel<T>, dim3(n), dim3(256), smem, stream, x, w, resid,
+                                       static_cast<T*>(rounded), hidden, eps, pair_row, pair_w, top));
   return launch_status();
 }

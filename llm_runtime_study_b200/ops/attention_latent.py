@@ -3,6 +3,7 @@ to the query's side)."""
 
 from __future__ import annotations
 
+import ctypes
 import os
 from typing import Any
 
@@ -21,7 +22,7 @@ _TABLE = {
     "b200_attention_latent_rank": [],
     "b200_attention_latent_rot": [],
     "b200_attention_latent_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int,
-                                   c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+                                   c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, ctypes.c_long, c_void_p],
 }
 
 
@@ -60,17 +61,34 @@ def latent_attention(q: torch.Tensor, pool: torch.Tensor, ctx: Any, table: torch
         return F.paged_attention_simt_latent(q, pool, value_dim=value_dim, positions=ctx.positions, token_entry=ctx.token_entry,
                                              block_table=table, scale=scale, window=window)
     per_tile = max(1, ROWS_PER_TILE // heads)
+    decode = ctx.all_decode and n == ctx.num_entries
     maps = ctx.__dict__.setdefault("_tile_maps", {})
     key = ("latent", per_tile)
     if key not in maps:
-        if ctx.all_decode and n == ctx.num_entries:
+        if decode:
             ramp = torch.arange(n, dtype=torch.int32, device=q.device)      # one tile a request, made on the device
             maps[key] = ((ramp, ramp, torch.ones_like(ramp)), n)
         else:
             maps[key] = attention_bf16.tile_map(ctx.q_lens, per_tile, q.device, ctx.kv_lens)
     tiles, count = maps[key]
     out = torch.empty((n, heads, value_dim), dtype=q.dtype, device=q.device)
+    splits, scratch, floats = 1, None, 0
+    if decode:
+        splits = decode_splits(n, heads, min(window, ctx.max_kv_len) if window else ctx.max_kv_len)
+        if splits > 1:
+            floats = n * heads * splits * (value_dim + 2)
+            scratch = torch.empty(floats, dtype=torch.float32, device=q.device)
     native.call("b200_attention_latent_bf16", q.data_ptr(), pool.data_ptr(), out.data_ptr(), ctx.positions.data_ptr(), table.data_ptr(),
                 table.shape[1], pool.shape[1], heads, float(scale), int(window), tiles[0].data_ptr(), tiles[1].data_ptr(),
-                tiles[2].data_ptr(), count, native.stream_ptr(), library=library_name(value_dim, rot))
+                tiles[2].data_ptr(), count, splits, native.ptr(scratch), floats, native.stream_ptr(),
+                library=library_name(value_dim, rot), launches=2 if splits > 1 else 1)
     return out
+
+
+def decode_splits(requests: int, heads: int, keys: int) -> int:
+    """Into how many parts a single token's keys are cut: enough CTAs for two a multiprocessor, no part shorter than four
+    tiles of 32 keys, at most 32 parts."""
+
+    ctas = requests * -(-heads // ROWS_PER_TILE)
+    wanted = -(-2 * native.sm_count() // max(ctas, 1))
+    return max(1, min(wanted, keys // 128, 32))

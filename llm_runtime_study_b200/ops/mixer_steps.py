@@ -6,8 +6,21 @@ from __future__ import annotations
 
 import torch
 
+from dataclasses import dataclass
+
 from ..errors import KernelError
 from .native import call, ptr, require, stream_ptr, tag
+
+
+@dataclass
+class PairedRows:
+    """A sublayer's output given in pieces: row ``t`` is ``sum_j weights[t, j] * rows[pair_row[t * top + j]]`` (what the experts a
+    router chose returned for token ``t``).  A consumer that reads the rows anyway forms the sum itself."""
+
+    rows: torch.Tensor          # float32 [sorted rows, width]
+    pair_row: torch.Tensor      # int32 [N * top]
+    weights: torch.Tensor       # float32 [N, top]
+
 
 
 def head_norm_write(
@@ -109,23 +122,33 @@ def sigmoid_gate(x: torch.Tensor, gate_rows: torch.Tensor, *, gate_offset: int, 
     return out
 
 
-def norm_accumulate_round(x: torch.Tensor | None, weight: torch.Tensor | None, eps: float, resid: torch.Tensor,
+def norm_accumulate_round(x: "torch.Tensor | PairedRows | None", weight: torch.Tensor | None, eps: float, resid: torch.Tensor,
                           rounded_dtype: torch.dtype | None) -> torch.Tensor | None:
     """``resid += x * rsqrt(mean(x^2) + eps) * weight`` in place on float32 rows (nothing is added when ``x`` is ``None``);
-    with ``rounded_dtype`` the updated rows are also returned in that type, for the sublayer that reads them next."""
+    with ``rounded_dtype`` the updated rows are also returned in that type, for the sublayer that reads them next.  ``x`` may be
+    ``PairedRows``: then row ``t`` of the sublayer's output is ``sum_j weights[t, j] * rows[pair_row[t, j]]``, formed inside the
+    kernel.  The width is at most 12,288 (a row is kept in shared memory)."""
 
     require(resid, "resid", dtype=torch.float32, dims=2)
     n, hidden = resid.shape
-    if x is not None:
+    pair_row = pair_w = None
+    top = 0
+    if isinstance(x, PairedRows):
+        pair_row, pair_w, top, x = x.pair_row, x.weights, x.weights.shape[1], x.rows
+        require(x, "rows", dtype=torch.float32, dims=2)
+        if x.shape[1] != hidden or pair_w.shape[0] != n:
+            raise KernelError("norm_accumulate_round: the paired rows do not fit the residual rows")
+    elif x is not None:
         require(x, "x", dtype=torch.float32, shape=resid.shape)
+    if x is not None:
         require(weight, "weight", dtype=torch.float32, shape=(hidden,))
     rounded = None
     if rounded_dtype is not None:
         rounded = torch.empty((n, hidden), dtype=rounded_dtype, device=resid.device)
     if x is None and rounded is None:
         return None
-    call("b200_norm_accumulate_round", ptr(x), ptr(weight), ptr(resid), ptr(rounded), n, hidden, float(eps),
-         tag(rounded_dtype or torch.float32), stream_ptr())
+    call("b200_norm_accumulate_round", ptr(x), ptr(weight), ptr(resid), ptr(rounded), n, hidden, float(eps), ptr(pair_row), ptr(pair_w),
+         top, tag(rounded_dtype or torch.float32), stream_ptr())
     return rounded
 
 

@@ -101,7 +101,8 @@ _LIBRARIES = {
             "b200_rope_slice": [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                 c_void_p, c_int, c_int, c_void_p],
             "b200_sigmoid_gate": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
-            "b200_norm_accumulate_round": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
+            "b200_norm_accumulate_round": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_int,
+                                           c_int, c_void_p],
         },
     ),
     "b200_rglru": (

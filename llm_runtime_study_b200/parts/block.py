@@ -132,7 +132,9 @@ class OutputNormBlock(Block):
         weight, eps = self.mixer_norm.fusable()
         x = M.norm_accumulate_round(out, weight, eps, resid, act if rounds else None)
         if self.feed_forward is not None:
-            out = self.feed_forward.forward(x if rounds else resid, ctx)
+            # a feed-forward that can hand over its experts' rows unsummed does: the norm's kernel forms the sum
+            pieces = {"pieces": True} if getattr(self.feed_forward, "returns_pieces", False) else {}
+            out = self.feed_forward.forward(x if rounds else resid, ctx, **pieces)
             weight, eps = self.ffn_norm.fusable()
             x = M.norm_accumulate_round(out, weight, eps, resid, act if rounds else None)
         if rounds:

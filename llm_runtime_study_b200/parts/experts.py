@@ -7,6 +7,7 @@ from typing import Any, Mapping
 import torch
 
 from ..ops import grouped as G
+from ..ops.mixer_steps import PairedRows
 from ..weights.checkpoint import TensorSpec
 from .base import FEED_FORWARDS, FeedForward, Runtime
 
@@ -49,9 +50,17 @@ class RoutedExperts(FeedForward):
         self.up = torch.stack([runtime.place_matrix(tensors[f"e{e}.up"]) for e in range(self.experts)])
         self.down = torch.stack([runtime.place_matrix(tensors[f"e{e}.down"]) for e in range(self.experts)])
 
-    def forward(self, x: torch.Tensor, ctx: Any) -> torch.Tensor:
+    # the weighted sum over a token's experts may be left to the consumer (``PairedRows``): see ``forward``
+    returns_pieces = True
+
+    def forward(self, x: torch.Tensor, ctx: Any, *, pieces: bool = False) -> "torch.Tensor | PairedRows":
+        """``pieces``: return the experts' rows with the pairing instead of their weighted sum, for a consumer that forms the
+        sum while it reads the rows anyway (the norm behind this part does)."""
+
         wide = G.wide_tiles_pay(x.shape[0], self.top, x.dtype, self.hidden_size, self.intermediate_size)
         routing = G.route(x, self.router, self.router_b, top=self.top, wide_tiles=wide)
         hidden = G.expert_linear(x, self.up, routing, gather=True, act=self.act)
         rows = G.expert_linear(hidden, self.down, routing, gather=False, out_dtype=torch.float32)
+        if pieces:
+            return PairedRows(rows, routing.pair_row, routing.weights)
         return G.combine(rows, routing)

@@ -160,7 +160,7 @@ def _latent_ctx(lengths, q_lens):
     positions = torch.cat([torch.arange(m - k, m) for m, k in zip(lengths, q_lens)]).int()
     entry = torch.cat([torch.full((k,), i) for i, k in enumerate(q_lens)]).int()
     return SimpleNamespace(positions=dev(positions), token_entry=dev(entry), all_decode=max(q_lens) == 1, num_entries=len(lengths),
-                           q_lens=list(q_lens), kv_lens=list(lengths)), positions, entry
+                           q_lens=list(q_lens), kv_lens=list(lengths), max_kv_len=max(lengths)), positions, entry
 
 
 @pytest.mark.parametrize("heads,rank,rot,page,window", [(3, 32, 16, 4, 9), (6, 64, 16, 16, 40), (16, 128, 64, 16, 0), (70, 48, 0, 8, 33),
@@ -192,6 +192,34 @@ def test_tensor_core_latent_attention(heads, rank, rot, page, window, q_lens):
         want = plain.softmax_attention(full_q, keys, keys[:, :, :rank], scale=0.3, window=window or None)[m - k:]
         assert (got[at:at + k] - want).abs().max() <= 2e-2 * max(1.0, float(want.abs().max())), (e, float((got[at:at + k] - want).abs().max()))
         at += k
+
+
+def test_single_tokens_whose_keys_are_cut_into_parts():
+    """Three requests of unequal length, one token each: the longest is cut into several parts and merged; a part may
+    hold no visible key at all (the short request)."""
+
+    from llm_runtime_study_b200.ops import attention_latent
+
+    torch.manual_seed(8)
+    heads, rank, rot, page = 6, 64, 16, 16
+    lengths, d = [1500, 3, 700], rank + rot
+    for window in (0, 600):
+        assert attention_latent.decode_splits(len(lengths), heads, min(window, max(lengths)) if window else max(lengths)) > 1
+        table, pages = _pages(window, page, lengths)
+        rows = [0.5 * torch.randn(m, d).bfloat16() for m in lengths]
+        pool = torch.zeros(pages, page, d, dtype=torch.bfloat16)
+        for e, m in enumerate(lengths):
+            for t in range(m):
+                pool[table[e, t // page], t % page] = rows[e][t]
+        ctx, _, _ = _latent_ctx(lengths, [1, 1, 1])
+        q = (0.5 * torch.randn(3, heads, d)).bfloat16()
+        got = attention_latent.latent_attention(dev(q), dev(pool), ctx, dev(table), value_dim=rank, scale=0.3, window=window).cpu().double()
+        for e, m in enumerate(lengths):
+            full_q = torch.zeros(m, heads, d, dtype=torch.float64)
+            full_q[m - 1] = q[e].double()
+            keys = rows[e].double()[:, None, :]
+            want = plain.softmax_attention(full_q, keys, keys[:, :, :rank], scale=0.3, window=window or None)[m - 1]
+            assert (got[e] - want).abs().max() <= 2e-2 * max(1.0, float(want.abs().max())), (window, e)
 
 
 @pytest.mark.parametrize("page,window,marked", [(16, 40, 15), (16, 40, 16), (8, 9, 63), (4, 5, 100), (16, 0, 3), (16, 64, 31), (16, 33, 32)])
@@ -376,6 +404,14 @@ def test_router_and_experts_against_plain(dtype, n, width, ff, experts, top):
     want = plain.moe(h.double(), {k: v.double() for k, v in weights.items()}, {"router": {"experts": experts, "top": top}}, store)
     tol = 2e-5 if dtype == torch.float32 else 2e-2
     assert (got - want).abs().max() <= tol * max(1.0, float(want.abs().max()))
+    # the norm behind the experts forms the weighted sum itself when it is handed the rows in pieces
+    from llm_runtime_study_b200.ops import mixer_steps as M
+
+    resid, w = torch.randn(n, width), 1 + 0.1 * torch.randn(width)
+    on_dev = dev(resid.clone())
+    M.norm_accumulate_round(M.PairedRows(rows, routing.pair_row, routing.weights), dev(w), 1e-5, on_dev, None)
+    want_resid = resid.double() + plain.rms_norm(got, w.double(), 1e-5)
+    assert (on_dev.cpu().double() - want_resid).abs().max() < 2e-5 * max(1.0, float(want_resid.abs().max()))
     # the sorted order: every pair has a row of its expert's tiles, padding rows belong to nobody
     tile = routing.tile_rows
     sorted_token, pair_row, tile_group = routing.sorted_token.cpu(), routing.pair_row.cpu(), routing.tile_group.cpu()

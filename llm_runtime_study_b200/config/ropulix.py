@@ -41,7 +41,7 @@ class LatentAttention:
     rot_dim: int
     vdim: int
     kv_rank: int
-    q_rank: int
+    q_rank: int          # 0: not in config.json; the stored shape of ``dq`` gives it
     scale: float
     window: int | None
     rot_base: float
@@ -109,7 +109,8 @@ def _mixer(kind: str, mixer: Mapping[str, Any], where: str):
         dim = _positive(mixer, "dim", where)
         return LatentAttention(
             _positive(mixer, "heads", where), dim, rot_dim, _positive(mixer, "vdim", where) if "vdim" in mixer else dim,
-            _positive(mixer, "kv_rank", where), _positive(mixer, "q_rank", where), float(required(mixer, "scale", NUMBER)),
+            _positive(mixer, "kv_rank", where), _positive(mixer, "q_rank", where) if "q_rank" in mixer else 0,
+            float(required(mixer, "scale", NUMBER)),
             _window(mixer, where), base, rot_dims, kv_from,
         )
     raise ConfigError(f"{where}: type {kind!r} is not a layer of this design; expected attention, rglru or latent_attention")

@@ -14,6 +14,7 @@ stored under the map's own name (no ``.weight``), its bias under ``<name>.b``.
 from __future__ import annotations
 
 from ..config.registry import Architecture, register_architecture
+from ..errors import ConfigError
 from ..config.ropulix import LatentAttention, Recurrence, RopulixConfig, RopulixLayer, WindowAttention
 from .description import LayerDescription, ModelDescription
 from .sorulix import stored_name
@@ -32,7 +33,7 @@ def _keep_window(index: int, config: RopulixConfig) -> int | None:
     return None if any(w is None for w in windows) else max(windows)
 
 
-def _mixer(index: int, layer: RopulixLayer, config: RopulixConfig) -> dict:
+def _mixer(index: int, layer: RopulixLayer, config: RopulixConfig, q_ranks: dict[int, int]) -> dict:
     m = layer.mixer
     if isinstance(m, WindowAttention):
         return {"kind": "gated_attention", "hidden_size": config.width, "num_heads": m.heads, "num_kv_heads": m.kv_heads,
@@ -41,20 +42,26 @@ def _mixer(index: int, layer: RopulixLayer, config: RopulixConfig) -> dict:
         return {"kind": "gated_linear_recurrence", "hidden_size": config.width, "width": m.width, "blocks": m.blocks,
                 "taps": m.conv, "decay_scale": DECAY_SCALE}
     assert isinstance(m, LatentAttention)
+    q_rank = m.q_rank or q_ranks.get(index, 0)
+    if q_rank <= 0:
+        raise ConfigError(f"layers[{index}].mixer.q_rank is neither in the configuration nor given by a stored tensor's shape")
     return {
         "kind": "latent_attention", "hidden_size": config.width, "num_heads": m.heads, "head_dim": m.dim, "rot_dim": m.rot_dim,
-        "value_dim": m.vdim, "kv_rank": m.kv_rank, "q_rank": m.q_rank, "eps": config.eps, "scale": m.scale, "window": m.window,
+        "value_dim": m.vdim, "kv_rank": m.kv_rank, "q_rank": q_rank, "eps": config.eps, "scale": m.scale, "window": m.window,
         "position": {"kind": "rope", "head_dim": m.rot_dim, "theta": m.rot_base, "rotary_dim": m.rot_dims} if m.rot_dims else None,
         "shares_kv": m.kv_from is not None, "keep_window": None if m.kv_from is not None else _keep_window(index, config),
     }
 
 
-def describe_ropulix(config: RopulixConfig) -> ModelDescription:
+def describe_ropulix(config: RopulixConfig, q_ranks: dict[int, int] | None = None) -> ModelDescription:
+    """``q_ranks``: per latent attention layer whose configuration does not name it, the query latent's size (the stored
+    shape of ``dq`` gives it: ``describe_for_checkpoint``)."""
+
     norm = {"kind": "rms_norm", "dim": config.width, "eps": config.eps}
     layers = []
     for i, layer in enumerate(config.layers):
         block = {
-            "kind": "output_norm", "mixer_norm": norm, "mixer": _mixer(i, layer, config),
+            "kind": "output_norm", "mixer_norm": norm, "mixer": _mixer(i, layer, config, q_ranks or {}),
             "ffn_norm": norm if layer.mlp else None,
             "feed_forward": {"kind": "routed_experts", "hidden_size": config.width, "intermediate_size": layer.mlp.ff,
                              "experts": layer.mlp.experts, "top": layer.mlp.top, "act": EXPERT_ACT} if layer.mlp else None,
@@ -73,8 +80,19 @@ def describe_ropulix(config: RopulixConfig) -> ModelDescription:
     )
 
 
+def describe_for_checkpoint(config: RopulixConfig, shapes) -> ModelDescription:
+    """The description with sizes that only the stored tensors give (``shapes``: name -> shape)."""
+
+    q_ranks = {}
+    for i, layer in enumerate(config.layers):
+        dq = shapes.get(f"l{i}.mix.dq")
+        if isinstance(layer.mixer, LatentAttention) and dq is not None and len(dq) == 2:
+            q_ranks[i] = int(dq[0])
+    return describe_ropulix(config, q_ranks)
+
+
 ROPULIX = Architecture(
     name=RopulixConfig.ARCHITECTURE, model_type=RopulixConfig.MODEL_TYPE,
-    config_from_dict=RopulixConfig.from_dict, describe=describe_ropulix,
+    config_from_dict=RopulixConfig.from_dict, describe=describe_ropulix, describe_for_checkpoint=describe_for_checkpoint,
 )
 register_architecture(ROPULIX, replace=True)

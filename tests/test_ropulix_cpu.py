@@ -141,3 +141,15 @@ def test_plain_convolution_recurrence_and_experts():
     p = math.exp(3) / (math.exp(3) + math.exp(2))
     assert abs(float(out) - (p * 4.0 + (1 - p) * 9.0)) < 1e-12
     assert float(plain.moe(torch.tensor([[-1.0]], dtype=torch.float64), w, m)) == 0.0       # relu shuts every expert
+
+
+def test_a_size_the_configuration_leaves_out_comes_from_the_stored_shapes():
+    from llm_runtime_study_b200.models.ropulix import describe_for_checkpoint
+
+    raw = copy.deepcopy(helpers.ROPULIX_B)
+    del raw["layers"][2]["mixer"]["q_rank"]
+    config = RopulixConfig.from_dict(raw)
+    with pytest.raises(ConfigError, match="q_rank"):
+        describe_ropulix(config)
+    schema = tensor_schema(describe_for_checkpoint(config, {"l2.mix.dq": (20, 48)}))
+    assert tuple(schema["l2.mix.dq"].shape) == (20, 48) and tuple(schema["l2.mix.uq"].shape) == (40, 20)

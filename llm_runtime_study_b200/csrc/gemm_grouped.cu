@@ -108,13 +108,18 @@ grouped_gemm_kernel(const GroupedArgs g) {
 // (110 KB in flight per CTA: what a few rows against a large weight need to stream it).  Eight warps,
 // two along the rows and four along the columns, each 32 x 32 outputs.  Every 16-byte chunk of A and W must start on a
 // 16-byte boundary: base pointers, row strides and batch strides are multiples of 8 elements (the launcher checks).
-constexpr int TBN = 128, TBK = 64, TPAD = 8, TSTAGES = 4;
+constexpr int TBK = 64, TPAD = 8, TSTAGES = 4;
 constexpr int TLD = TBK + TPAD;                         // 72 halves = 144 bytes a row: ldmatrix reads hit every bank once
-constexpr int TSTAGE_HALVES = (BM + TBN) * TLD;
 
-template <typename TOut, int ACT>
+// TBN columns a tile: 128, or 64 for launches of few tiles (single tokens against large weights), which then have twice the
+// CTAs and two of them on a multiprocessor.
+template <typename TOut, int ACT, int TBN>
 __global__ void __launch_bounds__(256)
 grouped_gemm_mma_kernel(const GroupedArgs g) {
+  constexpr int TSTAGE_HALVES = (BM + TBN) * TLD;
+  constexpr int WN = TBN / 4;             // columns of a warp
+  constexpr int NB = WN / 16;             // B fragments (16 columns each) a k step
+  constexpr int NJ = WN / 8;              // 8-column accumulator tiles
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* tiles = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __shared__ int src_row[BM];
@@ -158,7 +163,7 @@ grouped_gemm_mma_kernel(const GroupedArgs g) {
       cp_async_16(As + a_row * TLD + a_chunk, src, bytes);
     }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < TBN / 32; ++i) {
       const int c = tid + i * 256;
       const int row = c >> 3, chunk = (c & 7) * 8;
       const int n = n0 + row, k = k0 + chunk;
@@ -167,8 +172,8 @@ grouped_gemm_mma_kernel(const GroupedArgs g) {
       cp_async_16(Ws + row * TLD + chunk, src, bytes);
     }
   };
-  const int wm = (warp >> 2) * 32, wn = (warp & 3) * 32;
-  float acc[2][4][4] = {};
+  const int wm = (warp >> 2) * 32, wn = (warp & 3) * WN;
+  float acc[2][NJ][4] = {};
   const int k_tiles = (g.K + TBK - 1) / TBK;
 #pragma unroll
   for (int s = 0; s < TSTAGES - 1; ++s) {
@@ -184,17 +189,17 @@ grouped_gemm_mma_kernel(const GroupedArgs g) {
     const __nv_bfloat16* Ws = As + BM * TLD;
 #pragma unroll
     for (int kk = 0; kk < TBK; kk += 16) {
-      uint32_t a[2][4], b[2][4];
+      uint32_t a[2][4], b[NB][4];
 #pragma unroll
       for (int i = 0; i < 2; ++i)
         ldmatrix_x4(a[i], As + (wm + i * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * TLD + kk + (lane >> 4) * 8);
 #pragma unroll
-      for (int j = 0; j < 2; ++j)
+      for (int j = 0; j < NB; ++j)
         ldmatrix_x4(b[j], Ws + (wn + j * 16 + (lane & 7) + (lane >> 4) * 8) * TLD + kk + ((lane >> 3) & 1) * 8);
 #pragma unroll
       for (int i = 0; i < 2; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) mma_bf16(acc[i][j], a[i], b[j >> 1][(j & 1) * 2], b[j >> 1][(j & 1) * 2 + 1]);
+        for (int j = 0; j < NJ; ++j) mma_bf16(acc[i][j], a[i], b[j >> 1][(j & 1) * 2], b[j >> 1][(j & 1) * 2 + 1]);
     }
   }
   cp_async_wait<0>();
@@ -206,7 +211,7 @@ grouped_gemm_mma_kernel(const GroupedArgs g) {
       if (src_row[local] < 0) continue;
       const long long m = m0 + local;
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
+      for (int j = 0; j < NJ; ++j)
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const int n = n0 + wn + j * 8 + (lane & 3) * 2 + e;
@@ -221,20 +226,24 @@ grouped_gemm_mma_kernel(const GroupedArgs g) {
     }
 }
 
-template <typename TOut>
-int launch_grouped_mma(const GroupedArgs& g, int batch, int act, cudaStream_t stream) {
+template <typename TOut, int ACT, int TBN>
+int launch_grouped_mma_tile(const GroupedArgs& g, int batch, cudaStream_t stream) {
   dim3 grid((g.N + TBN - 1) / TBN, (g.M + BM - 1) / BM, batch);
   if (grid.y > 65535 || grid.z > 65535) return B200_ERR_TOO_LARGE;
-  constexpr size_t smem = sizeof(__nv_bfloat16) * TSTAGES * TSTAGE_HALVES;
-  static DeviceOnce once[2];
-  if (act == 1) {
-    if (int e = configure_once(once[1], grouped_gemm_mma_kernel<TOut, 1>, smem)) return e;
-    launch(grouped_gemm_mma_kernel<TOut, 1>, grid, dim3(256), smem, stream, g);
-  } else {
-    if (int e = configure_once(once[0], grouped_gemm_mma_kernel<TOut, 0>, smem)) return e;
-    launch(grouped_gemm_mma_kernel<TOut, 0>, grid, dim3(256), smem, stream, g);
-  }
+  constexpr size_t smem = sizeof(__nv_bfloat16) * TSTAGES * (BM + TBN) * TLD;
+  static DeviceOnce once;
+  if (int e = configure_once(once, grouped_gemm_mma_kernel<TOut, ACT, TBN>, smem)) return e;
+  launch(grouped_gemm_mma_kernel<TOut, ACT, TBN>, grid, dim3(256), smem, stream, g);
   return launch_status();
+}
+
+template <typename TOut>
+int launch_grouped_mma(const GroupedArgs& g, int batch, int act, cudaStream_t stream) {
+  // fewer tiles of 128 columns than multiprocessors (a B200 has 148): tiles of 64 columns
+  const long tiles = static_cast<long>((g.N + 127) / 128) * ((g.M + BM - 1) / BM) * batch;
+  const bool narrow = tiles < 148 && g.N > 64;
+  if (act == 1) return narrow ? launch_grouped_mma_tile<TOut, 1, 64>(g, batch, stream) : launch_grouped_mma_tile<TOut, 1, 128>(g, batch, stream);
+  return narrow ? launch_grouped_mma_tile<TOut, 0, 64>(g, batch, stream) : launch_grouped_mma_tile<TOut, 0, 128>(g, batch, stream);
 }
 
 // ----------------------------------------------------------------------------- router
@@ -257,11 +266,23 @@ route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float*
     float dot[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) dot[j] = 0.f;
-    for (int i = threadIdx.x; i < width; i += 128) {
-      const float x = to_float(row[i]);
+    if ((width & 3) == 0) {          // four columns a thread and pass: 16-byte loads of the router's rows
+      for (int i = threadIdx.x * 4; i < width; i += 512) {
+        const float x0 = to_float(row[i]), x1 = to_float(row[i + 1]), x2 = to_float(row[i + 2]), x3 = to_float(row[i + 3]);
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (e0 + j < experts) dot[j] = fmaf(x, wr[static_cast<size_t>(e0 + j) * width + i], dot[j]);
+        for (int j = 0; j < 8; ++j)
+          if (e0 + j < experts) {
+            const float4 w4 = *reinterpret_cast<const float4*>(wr + static_cast<size_t>(e0 + j) * width + i);
+            dot[j] = fmaf(x3, w4.w, fmaf(x2, w4.z, fmaf(x1, w4.y, fmaf(x0, w4.x, dot[j]))));
+          }
+      }
+    } else {
+      for (int i = threadIdx.x; i < width; i += 128) {
+        const float x = to_float(row[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (e0 + j < experts) dot[j] = fmaf(x, wr[static_cast<size_t>(e0 + j) * width + i], dot[j]);
+      }
     }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {

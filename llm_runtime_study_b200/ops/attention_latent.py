@@ -66,8 +66,7 @@ def latent_attention(q: torch.Tensor, pool: torch.Tensor, ctx: Any, table: torch
     key = ("latent", per_tile)
     if key not in maps:
         if decode:
-            ramp = torch.arange(n, dtype=torch.int32, device=q.device)      # one tile a request, made on the device
-            maps[key] = ((ramp, ramp, torch.ones_like(ramp)), n)
+            maps[key] = (_single_token_tiles(n, q.device), n)      # one tile a request
         else:
             maps[key] = attention_bf16.tile_map(ctx.q_lens, per_tile, q.device, ctx.kv_lens)
     tiles, count = maps[key]
@@ -83,6 +82,23 @@ def latent_attention(q: torch.Tensor, pool: torch.Tensor, ctx: Any, table: torch
                 tiles[2].data_ptr(), count, splits, native.ptr(scratch), floats, native.stream_ptr(),
                 library=library_name(value_dim, rot), launches=2 if splits > 1 else 1)
     return out
+
+
+_RAMPS: dict = {}
+
+
+def _single_token_tiles(n: int, device) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """(entry, first row, rows) of tiles that are token ``t`` alone: views of a ramp kept per device (made outside a graph
+    capture; inside one, where nothing may outlive the graph's pool, a ramp of its own)."""
+
+    if torch.cuda.is_current_stream_capturing():
+        ramp = torch.arange(n, dtype=torch.int32, device=device)
+        return ramp, ramp, torch.ones_like(ramp)
+    kept = _RAMPS.get(device)
+    if kept is None or kept[0].shape[0] < n:
+        size = max(n, 256)
+        kept = _RAMPS[device] = (torch.arange(size, dtype=torch.int32, device=device), torch.ones(size, dtype=torch.int32, device=device))
+    return kept[0][:n], kept[0][:n], kept[1][:n]
 
 
 def decode_splits(requests: int, heads: int, keys: int) -> int:

@@ -323,7 +323,20 @@ ROPULIX_C = {
          "mlp": {"kind": "moe", "expert": {"ff": 64}, "router": {"experts": 6, "top": 2}}},
     ],
 }
-ROPULIX = {"A": (ROPULIX_A, 21, 4), "B": (ROPULIX_B, 22, 16), "C": (ROPULIX_C, 23, 16)}   # config, seed, page size
+# D: no window anywhere (every key since the first token is read, through the kernels that take no mask), heads of 64 with
+# grouped key/value heads, a latent whose value size differs from the rows' width by 16, experts in two passes of eight.
+ROPULIX_D = {
+    "architecture": "Ropulix", "vocab": 173, "width": 128, "norm": {"eps": 1e-5},
+    "layers": [
+        {"type": "latent_attention", "mixer": {"heads": 2, "dim": 32, "rot_dim": 16, "vdim": 48, "kv_rank": 64, "q_rank": 64,
+                                               "rot": {"base": 30000.0, "dims": 16}, "scale": 0.15},
+         "mlp": {"kind": "moe", "expert": {"ff": 32}, "router": {"experts": 10, "top": 4}}},
+        {"type": "attention", "mixer": {"heads": 4, "kv_heads": 2, "dim": 64, "vdim": 64, "scale": 0.125},
+         "mlp": {"kind": "moe", "expert": {"ff": 32}, "router": {"experts": 10, "top": 4}}},
+        {"type": "rglru", "mixer": {"width": 160, "blocks": 5, "conv": 5}, "mlp": None},
+    ],
+}
+ROPULIX = {"A": (ROPULIX_A, 21, 4), "B": (ROPULIX_B, 22, 16), "C": (ROPULIX_C, 23, 16), "D": (ROPULIX_D, 24, 16)}   # config, seed, page size
 
 
 def make_ropulix_dir(path: Path, config: dict, seed: int, *, torch_dtype: str = "float32", gain: float = 6.0):

@@ -20,7 +20,7 @@ DEV = "cuda:0"
 # float32 is the sharp comparison.  bfloat16: the plain model rounds its activations where the engine stores them; a
 # rounding that falls the other way moves single rows by several per cent, so a request passes when at most a tenth of its
 # rows (or one) is beyond BF16_USUAL and none beyond BF16_WORST.  A row at which some router's last chosen logit lies within
-# CLOSE_CALL of the first one left out is not judged: there the two models may rightly send the token to different experts.
+# CLOSE_CALL of the first one left out is not compared: there the two models may rightly send the token to different experts.
 # A wrong state, slot or page moves every row after it; the kernels alone are compared sharply above.
 TOL = {"float32": (3e-5, 2e-4)}
 BF16_USUAL, BF16_WORST, CLOSE_CALL = 6e-2, 5e-1, 0.15
@@ -452,7 +452,7 @@ def test_batched_products_with_strides():
 
 
 # ------------------------------------------------------------------------------------------- whole models
-LENGTHS = {"A": [1, 2, 5, 23, 64, 65, 131], "B": [3, 17, 48, 70, 1, 129], "C": [140, 2, 37, 66, 300]}
+LENGTHS = {"A": [1, 2, 5, 23, 64, 65, 131], "B": [3, 17, 48, 70, 1, 129], "C": [140, 2, 37, 66, 300], "D": [200, 33, 40, 1, 90]}
 
 
 def _requests(name):
@@ -461,7 +461,7 @@ def _requests(name):
     return {f"r{i}": helpers.random_tokens(rng, config["vocab"], n) for i, n in enumerate(LENGTHS[name])}
 
 
-@pytest.fixture(scope="module", params=[(n, d) for n in ("A", "B") for d in ("float32", "bfloat16")] + [("C", "bfloat16")], ids=lambda p: f"{p[0]}-{p[1]}")
+@pytest.fixture(scope="module", params=[(n, d) for n in ("A", "B") for d in ("float32", "bfloat16")] + [("C", "bfloat16"), ("D", "bfloat16"), ("D", "float32")], ids=lambda p: f"{p[0]}-{p[1]}")
 def setup(request, tmp_path_factory):
     from llm_runtime_study_b200.engine.runtime import load
 
@@ -505,7 +505,7 @@ def _compare(setup, got, requests=None):
             err = (rows - want).pow(2).mean(dim=1).sqrt() / want.pow(2).mean(dim=1).sqrt()
             assert torch.isfinite(err).all()
             clear = setup["clear"][rid]
-            assert int(clear.sum()) >= len(tokens) // 2, "the weights make too many close calls for this test to judge anything"
+            assert int(clear.sum()) >= len(tokens) // 2, "the weights make too many close calls for this test to compare anything"
             err = torch.where(clear, err, torch.zeros_like(err))
             assert float(err.max()) <= BF16_WORST, (rid, int(err.argmax()), float(err.max()))
             over = int((err > BF16_USUAL).sum())
@@ -541,7 +541,7 @@ def test_mixed_batches_with_slots_and_pages_used_again(setup):
 def test_every_token_decoded_alone(setup):
     """A sequence fed one token a step from its first token: the first tokens, long decoding."""
 
-    requests = {rid: tokens for rid, tokens in setup["requests"].items() if len(tokens) in (23, 131, 70, 66)}
+    requests = {rid: tokens for rid, tokens in setup["requests"].items() if len(tokens) in (23, 131, 70, 66, 90)}
     _compare(setup, _replay(setup, helpers.trace_decode_tail(requests, tail=10_000)), requests)
 
 
@@ -558,7 +558,7 @@ def test_a_cut_changes_no_bit_in_float32(setup):
 def test_a_reused_slot_starts_from_zero(setup):
     """One slot: the second request takes the first one's state rows, convolution inputs and pages."""
 
-    requests = {rid: tokens for rid, tokens in setup["requests"].items() if len(tokens) in (23, 17, 48, 65, 37, 66)}
+    requests = {rid: tokens for rid, tokens in setup["requests"].items() if len(tokens) in (23, 17, 48, 65, 37, 66, 33, 90)}
     _compare(setup, _replay(setup, helpers.trace_chunked(requests, random.Random(3), sizes=(7, 16)), max_requests=1), requests)
 
 
